@@ -67,10 +67,14 @@ class CacheManager:
         for layer, need in enumerate(needs):
             if isinstance(need, KVCacheNeed):
                 for index, group in enumerate(groups):
-                    if (group.kv_heads, group.head_dim, group.window) == (need.kv_heads, need.head_dim, need.window):
+                    # (layers whose keys or values use other columns of a row do not share pages: the unused columns
+                    # of a page must stay zero for whoever gets it next)
+                    if (group.kv_heads, group.head_dim, group.window, group.key_dim, group.value_dim) == (
+                            need.kv_heads, need.head_dim, need.window, need.key_dim, need.value_dim):
                         break
                 else:
-                    groups.append(GroupSpec(need.kv_heads, need.head_dim, need.window))
+                    groups.append(GroupSpec(need.kv_heads, need.head_dim, need.window, key_dim=need.key_dim,
+                                            value_dim=need.value_dim))
                     index = len(groups) - 1
                 self._layer_place[layer] = ("kv", index, len(groups[index].layers))
                 groups[index].layers.append(layer)
@@ -144,7 +148,7 @@ class CacheManager:
 
     def bytes_per_token(self) -> int:
         element = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.layers) * 2 * g.kv_heads * g.head_dim * element for g in self.groups)
+        return sum(len(g.layers) * 2 * g.kv_heads * g.head_dim * element for g in self.groups)  # rows are stored whole
 
     def stats(self) -> dict:
         return self.tables.stats()

@@ -109,6 +109,8 @@ class GroupSpec:
     head_dim: int
     window: Optional[int]
     layers: List[int] = field(default_factory=list)  # cache-layer ids in this group
+    key_dim: Optional[int] = None    # columns of a row that keys use (None: all)
+    value_dim: Optional[int] = None  # columns of a row that values use (None: all)
 
 
 @dataclass(eq=False)

@@ -23,6 +23,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 SOURCES = [
     "elementwise.cu",
+    "layer_forms.cu",
+    "experts.cu",
     "gemm_simt.cu",
     "attention_plain.cu",
     "sampling.cu",

@@ -1,0 +1,287 @@
+// Row-wise kernels of layer forms beside the pre-norm / rotary ones of elementwise.cu:
+//
+//   * embedding rows times a constant, plus a sinusoidal position vector (column 2i the sine and column 2i + 1
+//     the cosine of position * frequency[i], angles in 32-bit);
+//   * the norm on a sub-layer's OUTPUT: stream += y / sqrt(mean(y^2) + eps) * w, with the runtime-dtype copy of the
+//     new stream that the next sub-layer reads written in the same pass;
+//   * the preparation of attention whose q, k, v projections carry biases and whose queries and keys are normed
+//     over the WHOLE projection (all heads of a token at once, one weight per column), with keys and values of
+//     their own widths: bias, norm, queries out (heads padded to the cache's head width), keys and values to their
+//     pages.
+//
+// Statistics, biases and norm weights are 32-bit; the products that feed these kernels leave 32-bit rows.
+#include "common.cuh"
+
+// ------------------------------------------------- scaled embedding + sinusoid
+template <typename T, typename C>
+__global__ void embedding_sinusoid_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                          const int* __restrict__ positions, const float* __restrict__ freq,
+                                          float* __restrict__ out, C* __restrict__ copy, int hidden, int vocab,
+                                          float scale, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int token = blockIdx.x;
+    const int id = ids[token];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(error_flag, KIRAI_FLAG_BAD_TOKEN);
+        return;
+    }
+    const float pos = freq ? (float)positions[token] : 0.0f;
+    const T* row = table + (size_t)id * hidden;
+    float* dst = out + (size_t)token * hidden;
+    C* dst_copy = copy ? copy + (size_t)token * hidden : nullptr;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = to_f32<T>(row[i]) * scale;
+        if (freq) {
+            const float angle = pos * freq[i >> 1];
+            v += (i & 1) ? cosf(angle) : sinf(angle);
+        }
+        dst[i] = v;
+        if (dst_copy) dst_copy[i] = from_f32<C>(v);
+    }
+}
+
+template <typename T>
+static int embedding_sinusoid_launch(const void* table, const int* ids, const int* positions, const float* freq,
+                                     float* out, void* copy, int tokens, int hidden, int vocab, float scale,
+                                     int* error_flag, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    return launch_pdl(embedding_sinusoid_kernel<T, bf16>, dim3(tokens), dim3(256), 0, stream, 1u, (const T*)table, ids,
+                      positions, freq, out, (bf16*)copy, hidden, vocab, scale, error_flag);
+}
+
+// out [T, H] (float32) = table[id] * scale (+ the sinusoid of the token's position when freq [ceil(H/2)] is given);
+// copy (bf16, may be null) receives the same rows rounded.
+KIRAI_EXPORT int kirai_embedding_sinusoid_f32(const void* table, const int* ids, const int* positions, const float* freq,
+                                              float* out, void* copy, int tokens, int hidden, int vocab, float scale,
+                                              int* error_flag, cudaStream_t stream) {
+    return embedding_sinusoid_launch<float>(table, ids, positions, freq, out, copy, tokens, hidden, vocab, scale, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_embedding_sinusoid_bf16(const void* table, const int* ids, const int* positions, const float* freq,
+                                               float* out, void* copy, int tokens, int hidden, int vocab, float scale,
+                                               int* error_flag, cudaStream_t stream) {
+    return embedding_sinusoid_launch<bf16>(table, ids, positions, freq, out, copy, tokens, hidden, vocab, scale, error_flag, stream);
+}
+
+// ------------------------------------------------------- norm on the output
+// One block per row: resid[row] += y[row] * rsqrt(mean(y[row]^2) + eps) * weight; copy[row] = bf16(resid[row]).
+__global__ void norm_add_kernel(float* __restrict__ resid, const float* __restrict__ y, const float* __restrict__ weight,
+                                bf16* __restrict__ copy, int hidden, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int row = blockIdx.x;
+    const float* src = y + (size_t)row * hidden;
+    float* dst = resid + (size_t)row * hidden;
+    bf16* dst_copy = copy ? copy + (size_t)row * hidden : nullptr;
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = src[i];
+        acc = fmaf(v, v, acc);
+    }
+    const float variance = block_sum(acc, scratch) / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = dst[i] + src[i] * scale * weight[i];
+        dst[i] = v;
+        if (dst_copy) dst_copy[i] = __float2bfloat16_rn(v);
+    }
+}
+
+// The same with 16-byte loads, the row of y kept in registers between the statistics and the add (width a multiple
+// of 4, at most 4 * VEC * blockDim values).
+template <int VEC>
+__global__ void norm_add_vec_kernel(float* __restrict__ resid, const float* __restrict__ y, const float* __restrict__ weight,
+                                    bf16* __restrict__ copy, int hidden, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int row = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(y + (size_t)row * hidden);
+    float4* dst = reinterpret_cast<float4*>(resid + (size_t)row * hidden);
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    const int quads = hidden >> 2;
+    float4 kept[VEC];
+    float acc = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < quads) {
+            kept[n] = src[i];
+            acc = fmaf(kept[n].x, kept[n].x, acc);
+            acc = fmaf(kept[n].y, kept[n].y, acc);
+            acc = fmaf(kept[n].z, kept[n].z, acc);
+            acc = fmaf(kept[n].w, kept[n].w, acc);
+        }
+    }
+    const float variance = block_sum(acc, scratch) / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < quads) {
+            float4 r = dst[i];
+            const float4 w = w4[i];
+            r.x += kept[n].x * scale * w.x;
+            r.y += kept[n].y * scale * w.y;
+            r.z += kept[n].z * scale * w.z;
+            r.w += kept[n].w * scale * w.w;
+            dst[i] = r;
+            if (copy) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(copy + (size_t)row * hidden + 4 * (size_t)i) = packed;
+            }
+        }
+    }
+}
+
+KIRAI_EXPORT int kirai_norm_add(float* resid, const float* y, const float* weight, void* copy, int rows, int hidden,
+                                float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0) return KIRAI_ERR_BAD_SIZE;
+    const bool aligned = hidden % 4 == 0 && (((uintptr_t)resid | (uintptr_t)y | (uintptr_t)weight | (uintptr_t)copy) & 15) == 0;
+    if (aligned && hidden <= 4 * 4 * 512) {
+        const int threads = hidden <= 4 * 4 * 128 ? 128 : (hidden <= 4 * 4 * 256 ? 256 : 512);
+        return launch_pdl(norm_add_vec_kernel<4>, dim3(rows), dim3(threads), 0, stream, 1u, resid, y, weight, (bf16*)copy, hidden, eps);
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    return launch_pdl(norm_add_kernel, dim3(rows), dim3(threads), 0, stream, 1u, resid, y, weight, (bf16*)copy, hidden, eps);
+}
+
+// ------------------------------------------------------------ 32-bit -> bf16
+__global__ void round_rows_kernel(const float* __restrict__ src, bf16* __restrict__ dst, long count) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) dst[i] = __float2bfloat16_rn(src[i]);
+}
+KIRAI_EXPORT int kirai_round_rows_bf16(const float* src, void* dst, long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    return launch_pdl(round_rows_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), 0, stream, 1u, src, (bf16*)dst, count);
+}
+
+// ------------------------------------- bias + norm over the whole projection + cache write
+// One block per token.  qkv [T, nq dk + nkv dk + nkv dv] (float32, as the stacked product left it; nkv = 0 for a layer
+// that reads another layer's keys and values).  Queries: + bias, times rsqrt(mean over all nq dk columns + eps) and
+// the column's weight, written to q_out [T, nq, dpad] (columns dk.. of a head zero).  Keys the same over their nkv dk
+// columns, written to the token's page row (first dk columns of the cache's dpad); values + bias to theirs (first dv
+// columns).  The cache is [pages, 2, nkv, page, dpad]; its columns beyond dk and dv are never written and stay zero
+// from creation.  A null bias adds nothing, a null norm weight leaves the rows unnormed.
+template <typename T>
+__global__ void qkv_wide_norm_write_kernel(const float* __restrict__ qkv, long qkv_stride, const float* __restrict__ q_bias,
+                                           const float* __restrict__ k_bias, const float* __restrict__ v_bias,
+                                           const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                                           T* __restrict__ q_out, T* __restrict__ cache, const int* __restrict__ block_table,
+                                           const int* __restrict__ request_of_token, const int* __restrict__ positions,
+                                           int q_heads, int kv_heads, int dk, int dv, int dpad, int page_size,
+                                           int table_width, int num_pages, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    extern __shared__ float row_s[];  // [nq dk + nkv dk]
+    __shared__ float scratch[32];
+    const int token = blockIdx.x;
+    const int q_cols = q_heads * dk, k_cols = kv_heads * dk, v_cols = kv_heads * dv;
+    // where this token's keys and values go: known before the product that made qkv has ended
+    long page_base = -1;
+    if (kv_heads > 0) {
+        const int pos = positions[token];
+        const int logical = pos / page_size;
+        const int page = logical < table_width ? block_table[(long)request_of_token[token] * table_width + logical] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(error_flag, KIRAI_FLAG_NO_PAGE_WRITE);
+        } else {
+            page_base = (((long)page * 2) * kv_heads * page_size + (pos % page_size)) * (long)dpad;
+        }
+    }
+    pdl_wait();
+    const float* src = qkv + (size_t)token * qkv_stride;
+    float q_acc = 0.0f, k_acc = 0.0f;
+    for (int i = threadIdx.x; i < q_cols + k_cols; i += blockDim.x) {
+        const bool is_q = i < q_cols;
+        const float* bias = is_q ? q_bias : k_bias;
+        const float v = src[i] + (bias ? bias[is_q ? i : i - q_cols] : 0.0f);
+        row_s[i] = v;
+        if (is_q) q_acc = fmaf(v, v, q_acc);
+        else k_acc = fmaf(v, v, k_acc);
+    }
+    const float q_total = block_sum(q_acc, scratch);
+    const float k_total = kv_heads > 0 ? block_sum(k_acc, scratch) : 0.0f;
+    __syncthreads();
+    float q_scale = 1.0f, k_scale = 1.0f;
+    if (q_weight) {
+        const float variance = q_total / (float)q_cols + eps;
+        q_scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    }
+    if (k_weight && kv_heads > 0) {
+        const float variance = k_total / (float)k_cols + eps;
+        k_scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    }
+    T* q_dst = q_out + (size_t)token * q_heads * dpad;
+    for (int i = threadIdx.x; i < q_heads * dpad; i += blockDim.x) {
+        const int head = i / dpad, c = i - head * dpad;
+        float v = 0.0f;
+        if (c < dk) {
+            const int col = head * dk + c;
+            v = row_s[col] * q_scale * (q_weight ? q_weight[col] : 1.0f);
+        }
+        q_dst[i] = from_f32<T>(v);
+    }
+    if (page_base < 0) return;
+    const long head_rows = (long)page_size * dpad;  // from one kv head's rows of a page to the next head's
+    for (int i = threadIdx.x; i < k_cols; i += blockDim.x) {
+        const int head = i / dk, c = i - head * dk;
+        cache[page_base + head * head_rows + c] = from_f32<T>(row_s[q_cols + i] * k_scale * (k_weight ? k_weight[i] : 1.0f));
+    }
+    const long value_base = page_base + (long)kv_heads * head_rows;
+    for (int i = threadIdx.x; i < v_cols; i += blockDim.x) {
+        const int head = i / dv, c = i - head * dv;
+        const float v = src[q_cols + k_cols + i] + (v_bias ? v_bias[i] : 0.0f);
+        cache[value_base + head * head_rows + c] = from_f32<T>(v);
+    }
+}
+
+template <typename T>
+static int qkv_wide_norm_write_launch(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias,
+                                      const float* v_bias, const float* q_weight, const float* k_weight, float eps,
+                                      void* q_out, void* cache, const int* block_table, const int* request_of_token,
+                                      const int* positions, int tokens, int q_heads, int kv_heads, int dk, int dv, int dpad,
+                                      int page_size, int table_width, int num_pages, int* error_flag, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (q_heads <= 0 || kv_heads < 0 || dk <= 0 || dv <= 0 || dpad < dk || dpad < dv || page_size <= 0) return KIRAI_ERR_BAD_SIZE;
+    if (kv_heads > 0 && !cache) return KIRAI_ERR_BAD_SIZE;
+    const size_t smem = (size_t)(q_heads + kv_heads) * dk * sizeof(float);
+    if (smem > 200 * 1024) return KIRAI_ERR_BAD_SIZE;
+    auto kernel = qkv_wide_norm_write_kernel<T>;
+    if (smem > 48 * 1024) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+    }
+    const int cols = (q_heads + kv_heads) * dk;
+    const int threads = cols >= 4096 ? 512 : (cols >= 1024 ? 256 : 128);
+    return launch_pdl(kernel, dim3(tokens), dim3(threads), smem, stream, 1u, qkv, qkv_stride, q_bias, k_bias, v_bias, q_weight,
+                      k_weight, eps, (T*)q_out, (T*)cache, block_table, request_of_token, positions, q_heads, kv_heads, dk, dv,
+                      dpad, page_size, table_width, num_pages, error_flag);
+}
+
+KIRAI_EXPORT int kirai_qkv_wide_norm_write_f32(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias,
+                                               const float* v_bias, const float* q_weight, const float* k_weight, float eps,
+                                               void* q_out, void* cache, const int* block_table, const int* request_of_token,
+                                               const int* positions, int tokens, int q_heads, int kv_heads, int dk, int dv,
+                                               int dpad, int page_size, int table_width, int num_pages, int* error_flag,
+                                               cudaStream_t stream) {
+    return qkv_wide_norm_write_launch<float>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_weight, k_weight, eps, q_out, cache,
+                                             block_table, request_of_token, positions, tokens, q_heads, kv_heads, dk, dv, dpad,
+                                             page_size, table_width, num_pages, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_qkv_wide_norm_write_bf16(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias,
+                                                const float* v_bias, const float* q_weight, const float* k_weight, float eps,
+                                                void* q_out, void* cache, const int* block_table, const int* request_of_token,
+                                                const int* positions, int tokens, int q_heads, int kv_heads, int dk, int dv,
+                                                int dpad, int page_size, int table_width, int num_pages, int* error_flag,
+                                                cudaStream_t stream) {
+    return qkv_wide_norm_write_launch<bf16>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_weight, k_weight, eps, q_out, cache,
+                                            block_table, request_of_token, positions, tokens, q_heads, kv_heads, dk, dv, dpad,
+                                            page_size, table_width, num_pages, error_flag, stream);
+}

@@ -236,6 +236,106 @@ def rope_(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rota
     return x
 
 
+# ------------------------------------------------- forms of other layer designs
+def embedding_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float, positions: Optional[torch.Tensor] = None,
+                     frequencies: Optional[torch.Tensor] = None, copy_dtype: Optional[torch.dtype] = None):
+    """Rows ``ids`` of the row-major ``table`` [V, H] times ``scale`` as the 32-bit stream [T, H]; with ``frequencies``
+    [ceil(H / 2)] (float32) the sinusoid of each token's position is added: column 2i gets sin(position * f_i), column
+    2i + 1 the cosine.  Returns (stream, copy): ``copy`` is the stream rounded to bfloat16 when ``copy_dtype`` asks for
+    it, else None."""
+    _need_cuda(table, ids, positions, frequencies)
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and table.dim() == 2 and table.is_contiguous()
+    tokens, hidden = ids.numel(), table.shape[1]
+    if frequencies is not None:
+        assert positions is not None and positions.dtype == torch.int32 and positions.numel() == tokens and positions.is_contiguous()
+        assert frequencies.dtype == torch.float32 and frequencies.numel() == (hidden + 1) // 2 and frequencies.is_contiguous()
+    out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    copy = None
+    if copy_dtype == torch.bfloat16:
+        copy = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=table.device)
+    _call(f"kirai_embedding_sinusoid_{_suffix(table.dtype)}", _ptr(table), _ptr(ids), _ptr(positions), _ptr(frequencies),
+          _ptr(out), _ptr(copy), _i(tokens), _i(hidden), _i(table.shape[0]), _f(scale), _ptr(error_flag(table.device)), _stream())
+    return out, copy
+
+
+def norm_add(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, copy_dtype: Optional[torch.dtype] = None):
+    """The norm on a sub-layer's output: ``resid`` (32-bit, in place) += RMSNorm(``y``) with ``weight``; ``y`` [T, H] is
+    32-bit.  Returns the new stream rounded to bfloat16 when ``copy_dtype`` asks for it (what the next sub-layer
+    reads), else None."""
+    _need_cuda(resid, y, weight)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    assert y.dtype == torch.float32 and y.shape == resid.shape and y.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.numel() == resid.shape[1] and weight.is_contiguous()
+    copy = torch.empty(resid.shape, dtype=torch.bfloat16, device=resid.device) if copy_dtype == torch.bfloat16 else None
+    _call("kirai_norm_add", _ptr(resid), _ptr(y), _ptr(weight), _ptr(copy), _i(resid.shape[0]), _i(resid.shape[1]), _f(eps), _stream())
+    return copy
+
+
+def round_rows(x: torch.Tensor) -> torch.Tensor:
+    """The 32-bit rows ``x`` rounded to bfloat16."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _call("kirai_round_rows_bf16", _ptr(x), _ptr(out), _l(x.numel()), _stream())
+    return out
+
+
+def qkv_wide_norm_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim: int, value_dim: int, pad_dim: int,
+                        q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor], v_bias: Optional[torch.Tensor],
+                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                        cache: Optional[torch.Tensor], block_table: torch.Tensor, request_of_token: torch.Tensor,
+                        positions: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Prepares attention whose queries and keys are normed over the whole projection: ``qkv`` [T, nq dk + nkv dk +
+    nkv dv] (float32, the stacked product; ``kv_heads`` 0 for a layer that projects queries only) gets its biases, the
+    queries and the keys are divided by the root mean square over ALL their columns and multiplied by a weight per
+    column, keys and values go to the token's page row in ``cache`` [pages, 2, nkv, page, pad_dim] (first dk and dv
+    columns), and the queries come back as [T, nq, pad_dim] in ``out_dtype`` with zero columns beyond dk."""
+    _need_cuda(qkv, q_bias, k_bias, v_bias, q_weight, k_weight, cache, block_table, request_of_token, positions)
+    assert qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.stride(1) == 1
+    assert qkv.shape[1] == q_heads * key_dim + kv_heads * (key_dim + value_dim)
+    for t, n in ((q_bias, q_heads * key_dim), (k_bias, kv_heads * key_dim), (v_bias, kv_heads * value_dim),
+                 (q_weight, q_heads * key_dim), (k_weight, kv_heads * key_dim)):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == n and t.is_contiguous())
+    num_pages, page_size = 0, 1
+    if kv_heads:
+        num_pages, c_heads, page_size, c_dim = _cache_dims(cache)
+        assert (c_heads, c_dim) == (kv_heads, pad_dim) and cache.dtype == out_dtype
+    tokens = qkv.shape[0]
+    q_out = torch.empty((tokens, q_heads, pad_dim), dtype=out_dtype, device=qkv.device)
+    _call(f"kirai_qkv_wide_norm_write_{_suffix(out_dtype)}", _ptr(qkv), _l(qkv.stride(0)), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+          _ptr(q_weight), _ptr(k_weight), _f(eps), _ptr(q_out), _ptr(cache if kv_heads else None), _ptr(block_table),
+          _ptr(request_of_token), _ptr(positions), _i(tokens), _i(q_heads), _i(kv_heads), _i(key_dim), _i(value_dim), _i(pad_dim),
+          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _ptr(error_flag(qkv.device)), _stream())
+    return q_out
+
+
+def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: bool = False):
+    """Routing weights of every token: logits ``router`` [experts, H] (float32) times ``x`` [T, H] in 32-bit, the ``top``
+    largest chosen (the lower index on a tie), softmax over the chosen logits alone.  Returns gates [T, experts]
+    (float32, zero where not chosen); with ``want_chosen`` also (ids [T, top] int32, weights [T, top] float32) in the
+    order of choice."""
+    _need_cuda(x, router)
+    assert x.dim() == 2 and x.stride(1) == 1 and router.dtype == torch.float32 and router.is_contiguous()
+    assert router.shape[1] == x.shape[1] and 0 < top <= router.shape[0]
+    tokens, experts = x.shape[0], router.shape[0]
+    gates = torch.empty((tokens, experts), dtype=torch.float32, device=x.device)
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device) if want_chosen else None
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device) if want_chosen else None
+    _call(f"kirai_router_gates_{_suffix(x.dtype)}", _ptr(x), _l(x.stride(0)), _ptr(router), _ptr(gates), _ptr(ids), _ptr(weights),
+          _i(tokens), _i(x.shape[1]), _i(experts), _i(top), _stream())
+    return (gates, ids, weights) if want_chosen else gates
+
+
+def relu2_gate_(up: torch.Tensor, gates: torch.Tensor, ff: int) -> torch.Tensor:
+    """In place on ``up`` [T, experts * ff]: relu(z)^2 times the token's gate of the column's expert."""
+    _need_cuda(up, gates)
+    assert up.dim() == 2 and up.is_contiguous() and gates.dtype == torch.float32 and gates.is_contiguous()
+    experts = gates.shape[1]
+    assert up.shape == (gates.shape[0], experts * ff)
+    _call(f"kirai_relu2_gate_{_suffix(up.dtype)}", _ptr(up), _ptr(gates), _i(up.shape[0]), _i(experts), _i(ff), _stream())
+    return up
+
+
 # ------------------------------------------------------------------- cache write
 def _cache_dims(cache: torch.Tensor):
     assert cache.dim() == 5 and cache.shape[1] == 2 and cache.is_contiguous(), "cache layer is [pages, 2, kv_heads, page, d]"

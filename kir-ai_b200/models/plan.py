@@ -16,7 +16,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..parts.base import Norm, Runtime, WeightSpec
+from ..parts.base import Norm, Runtime, StreamCopy, WeightSpec
 from ..parts.block import Block
 from ..parts.embedding import Embedding, OutputHead
 
@@ -118,7 +118,11 @@ class DecoderModel:
         """The residual stream [T, H] (32-bit) and the last block's not-yet-added output."""
         nvtx = torch.cuda.nvtx if self.nvtx else None  # ranges around the layer calls, for a timeline tool
         with self.rt.ops.chained_products(self._kernels_only):
-            resid = self.plan.embedding.forward(batch.token_ids)
+            embedding = self.plan.embedding
+            if getattr(embedding, "uses_positions", False):
+                resid = embedding.forward(batch.token_ids, batch.positions)
+            else:
+                resid = embedding.forward(batch.token_ids)
             delta = None
             order = self.plan.order
             for i, call in enumerate(order):
@@ -133,6 +137,8 @@ class DecoderModel:
 
     def logits(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """32-bit logits [len(rows), V] of the token rows ``rows`` (int32, on the device)."""
+        if isinstance(delta, StreamCopy):
+            delta = None  # the last block left the stream complete
         with self.rt.ops.chained_products(self._kernels_only):
             normed = self.plan.final_norm.add_forward_rows(resid, delta, rows)
             logits = self.plan.head.forward(normed)

@@ -1,12 +1,13 @@
 """The parts a model is put together from (see ``base`` for the interfaces)."""
 from .attention import GQAttention
-from .base import (FeedForward, KVCacheNeed, Mixer, Norm, Part, PositionEncoding, Runtime, StateNeed, WeightSpec)
+from .base import (FeedForward, KVCacheNeed, Mixer, Norm, Part, PositionEncoding, Runtime, StateNeed, StreamCopy, WeightSpec)
 from .block import Block
 from .embedding import Embedding, OutputHead
+from .experts import RoutedExperts
 from .linear import Linear
 from .norm import RMSNorm
 from .rope import RotaryEmbedding
 from .swiglu import SwiGLU
 
 __all__ = ["GQAttention", "FeedForward", "KVCacheNeed", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime",
-           "StateNeed", "WeightSpec", "Block", "Embedding", "OutputHead", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLU"]
+           "StateNeed", "StreamCopy", "WeightSpec", "RoutedExperts", "Block", "Embedding", "OutputHead", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLU"]

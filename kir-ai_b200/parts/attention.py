@@ -13,6 +13,19 @@ see rows [i - W + 1, i].
 Every size and constant is a constructor argument; the position encoding is a
 part of its own.  A layer built with ``reads_only`` has no k and v projections:
 it projects q alone and reads a cache that another layer filled.
+
+Three further options, each a constructor argument: ``value_dim`` (values of
+another width than queries and keys; the output projection then reads
+heads * value_dim columns), ``bias`` (q, k and v carry biases, added with the
+projection), and ``qk_norm_over="projection"``: the RMS norm runs over ALL
+columns of a token's q (and of its k) at once, before the split into heads,
+with one weight per column, where ``"head"`` norms each head with a shared
+weight [d].  A layer with any of the three takes one preparation kernel (bias,
+norm, queries out, keys and values to their pages) and then the same attention
+kernels; cache rows are max(head_dim, value_dim) wide, rounded up to 8, the
+unused columns zero, and the output projection's matrix gets zero columns where
+a head's output is padding.  ``out_dtype`` is the dtype of the mixer's result
+(default: the runtime's).
 """
 from __future__ import annotations
 
@@ -29,28 +42,51 @@ class GQAttention(Mixer):
     def __init__(self, prefix: str, hidden_size: int, q_heads: int, kv_heads: int, head_dim: int,
                  position: Optional[PositionEncoding], *, window: Optional[int] = None,
                  qk_norm_eps: Optional[float] = None, scale: Optional[float] = None, reads_only: bool = False,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, value_dim: Optional[int] = None, bias: bool = False,
+                 qk_norm_over: str = "head", out_dtype: Optional[torch.dtype] = None):
         if q_heads % kv_heads:
             raise ValueError(f"{q_heads} query heads are not a multiple of {kv_heads} kv heads")
+        if qk_norm_over not in ("head", "projection"):
+            raise ValueError(f"qk_norm_over must be 'head' or 'projection', got {qk_norm_over!r}")
         n = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
+             "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias"}
         n.update(names or {})
         self.prefix = prefix
         self.hidden_size, self.q_heads, self.kv_heads, self.head_dim = hidden_size, q_heads, kv_heads, head_dim
+        self.value_dim = head_dim if value_dim is None else value_dim
         self.window = window
         self.qk_norm_eps = qk_norm_eps
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.position = position
         self.reads_only = reads_only
+        self.bias = bias
+        self.out_dtype = out_dtype
+        # the preparation that takes biases, a norm over the whole projection and values of their own width
+        self.wide = bias or self.value_dim != head_dim or (qk_norm_eps is not None and qk_norm_over == "projection")
+        self.norm_over_projection = qk_norm_eps is not None and qk_norm_over == "projection"
+        self.pad_dim = head_dim
+        if self.wide:
+            if position is not None:
+                raise ValueError("a position encoding on queries and keys is not built for attention with biases, a norm "
+                                 "over the whole projection or values of their own width")
+            if qk_norm_eps is not None and qk_norm_over == "head":
+                raise ValueError("a per-head q/k norm is not built together with biases or values of their own width")
+            self.pad_dim = -(-max(head_dim, self.value_dim) // 8) * 8
         sources = [(prefix + n["q"], q_heads * head_dim)]
         if not reads_only:
-            sources += [(prefix + n["k"], kv_heads * head_dim), (prefix + n["v"], kv_heads * head_dim)]
+            sources += [(prefix + n["k"], kv_heads * head_dim), (prefix + n["v"], kv_heads * self.value_dim)]
         self.qkv = Linear(sources, hidden_size)
-        self.out = Linear([(prefix + n["o"], hidden_size)], q_heads * head_dim)
+        self.out = Linear([(prefix + n["o"], hidden_size)], q_heads * self.value_dim,
+                          column_groups=(q_heads, self.value_dim, self.pad_dim) if self.wide else None)
         self.q_norm_name, self.k_norm_name = prefix + n["q_norm"], prefix + n["k_norm"]
+        self.bias_names = (prefix + n["q_bias"], prefix + n["k_bias"], prefix + n["v_bias"])
         self.q_norm_weight = self.k_norm_weight = None
+        self.q_bias = self.k_bias = self.v_bias = None
 
     def cache_need(self):
+        if self.wide:
+            return KVCacheNeed(self.kv_heads, self.pad_dim, self.window, key_dim=self.head_dim, value_dim=self.value_dim)
         return KVCacheNeed(self.kv_heads, self.head_dim, self.window)
 
     @property
@@ -66,9 +102,15 @@ class GQAttention(Mixer):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs = {**self.qkv.weight_specs(), **self.out.weight_specs()}
         if self.qk_norm_eps is not None:
-            specs[self.q_norm_name] = WeightSpec((self.head_dim,), "norm")
+            over = (self.q_heads, self.kv_heads) if self.norm_over_projection else (1, 1)
+            specs[self.q_norm_name] = WeightSpec((over[0] * self.head_dim,), "norm")
             if not self.reads_only:
-                specs[self.k_norm_name] = WeightSpec((self.head_dim,), "norm")
+                specs[self.k_norm_name] = WeightSpec((over[1] * self.head_dim,), "norm")
+        if self.bias:
+            specs[self.bias_names[0]] = WeightSpec((self.q_heads * self.head_dim,), "bias")
+            if not self.reads_only:
+                specs[self.bias_names[1]] = WeightSpec((self.kv_heads * self.head_dim,), "bias")
+                specs[self.bias_names[2]] = WeightSpec((self.kv_heads * self.value_dim,), "bias")
         if self.position is not None:
             specs.update(self.position.weight_specs())
         return specs
@@ -81,17 +123,35 @@ class GQAttention(Mixer):
             self.q_norm_weight = weights.on_device(self.q_norm_name, torch.float32)
             if not self.reads_only:
                 self.k_norm_weight = weights.on_device(self.k_norm_name, torch.float32)
+        if self.bias:
+            self.q_bias = weights.on_device(self.bias_names[0], torch.float32)
+            if not self.reads_only:
+                self.k_bias = weights.on_device(self.bias_names[1], torch.float32)
+                self.v_bias = weights.on_device(self.bias_names[2], torch.float32)
         if self.position is not None:
             self.position.load(weights, rt)
 
     def takes_unscaled(self, rows: int) -> bool:
-        return self.qkv.fuses_norms(rows)
+        return not self.wide and self.qkv.fuses_norms(rows)
 
     def fuses_into_norm(self, rows: int) -> bool:
         return self.out.fuses_norms(rows)
 
     def forward(self, x, batch, cache, write_cache: bool = True) -> torch.Tensor:
-        return self.out.forward(self._mix(x, batch, cache, write_cache))
+        return self.out.forward(self._mix(x, batch, cache, write_cache), self.out_dtype)
+
+    def _mix_wide(self, x, batch, cache, write_cache: bool) -> torch.Tensor:
+        """[T, q_heads * pad_dim]: the stacked product in 32-bit, one preparation kernel, the attention kernels."""
+        ops = self.rt.ops
+        nkv = 0 if self.reads_only else self.kv_heads
+        if nkv and not write_cache:
+            raise ValueError("an attention layer with k and v projections of its own must fill its cache")
+        table = batch.block_tables[cache.group]
+        qkv = self.qkv.forward(x, torch.float32)
+        q = ops.qkv_wide_norm_write(qkv, self.q_heads, nkv, self.head_dim, self.value_dim, self.pad_dim, self.q_bias,
+                                    self.k_bias, self.v_bias, self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps or 0.0,
+                                    cache.kv, table, batch.request_of_token, batch.positions, self.rt.dtype)
+        return ops.paged_attention(q, cache.kv, table, batch, self.window, self.scale)
 
     def forward_into_norm(self, x, batch, cache, write_cache, resid, spec):
         return self.out.forward_into_norm(self._mix(x, batch, cache, write_cache), resid, spec)
@@ -103,6 +163,8 @@ class GQAttention(Mixer):
         nkv = 0 if self.reads_only else self.kv_heads  # kv heads that this layer projects
         if write_cache and self.reads_only:
             raise ValueError("a reads_only attention layer cannot fill a cache")
+        if self.wide:
+            return self._mix_wide(x, batch, cache, write_cache)
         table = batch.block_tables[cache.group]
         qkv = self.qkv.forward(x)  # [T, (nq + 2 nkv) d]
         fused_table = self.position.fused_table() if isinstance(self.position, RotaryEmbedding) else None

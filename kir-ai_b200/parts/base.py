@@ -35,11 +35,16 @@ class WeightSpec:
 @dataclass(frozen=True)
 class KVCacheNeed:
     """A mixer that keeps keys and values of earlier tokens in pages.
-    ``window`` None keeps every token; a width W keeps the last W."""
+    ``window`` None keeps every token; a width W keeps the last W.  ``head_dim`` is the width of a
+    cache row.  Keys and values may be narrower than the row and differ from each other
+    (``key_dim``, ``value_dim``; None: the whole row): the columns beyond them are never written
+    and stay zero, so kernels that read whole rows compute the same scores and sums."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    key_dim: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -72,6 +77,15 @@ class UnscaledNorm:
 
     def row_scale(self):
         return (self.sumsq, self.width, self.eps)
+
+
+@dataclass
+class StreamCopy:
+    """What a block leaves when nothing is left to add: the stream is complete, and ``rows`` is its
+    copy in the runtime dtype (None when the runtime dtype is the stream's own), which the next
+    sub-layer may read instead of rounding the stream again."""
+
+    rows: Optional[torch.Tensor] = None
 
 
 class Runtime:
@@ -137,6 +151,11 @@ class Norm(Part):
         """Optional: what the product before this norm needs to take it over (see ``Block``); None keeps
         the norm a kernel of its own."""
         return None
+
+    def add_normed(self, resid: torch.Tensor, y: torch.Tensor) -> Optional[torch.Tensor]:
+        """For a block that norms a sub-layer's OUTPUT: ``resid`` (32-bit, in place) += norm(``y``), ``y`` 32-bit.
+        Returns the new stream in the runtime dtype, or None when that is the stream's own dtype."""
+        raise NotImplementedError
 
 
 class PositionEncoding(Part):

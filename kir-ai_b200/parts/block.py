@@ -5,7 +5,12 @@ runtime dtype) is added into it by the next norm, so that sum and norm are one
 pass over the row.  ``pre_norm`` is the reference's order
 (crates/llm-backend/src/core/qwen/ops/decoder.rs:210-314): n1 = norm1(h);
 a = mixer(n1); n2 = norm2(h + a); m = ffn(n2); out = h + a + m.  ``parallel``
-feeds one norm to both sub-layers: out = h + mixer(n) + ffn(n).
+feeds one norm to both sub-layers: out = h + mixer(n) + ffn(n).  ``out_norm``
+norms what a sub-layer produced, not what it reads: h' = h + norm1(mixer(h));
+out = h' + norm2(ffn(h')), the sub-layers reading the stream itself (rounded to
+the runtime dtype); such a block may have no feed-forward (``ffn`` and ``norm2``
+None), and it asks its sub-layers for 32-bit outputs (``out_dtype``), which the
+norm kernel reads.
 
 Where the parts on both sides offer it, a norm is not a kernel of its own: the product before it adds into the
 stream and writes the norm's rows without their 1 / rms factor (``forward_into_norm``), and the product after it
@@ -18,9 +23,9 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, FusedNormSpec, Mixer, Norm, Part, Runtime, UnscaledNorm, WeightSpec
+from .base import FeedForward, FusedNormSpec, Mixer, Norm, Part, Runtime, StreamCopy, UnscaledNorm, WeightSpec
 
-ARRANGEMENTS = ("pre_norm", "parallel")
+ARRANGEMENTS = ("pre_norm", "parallel", "out_norm")
 
 
 def _offers(part, method: str, rows: int) -> bool:
@@ -31,11 +36,15 @@ def _offers(part, method: str, rows: int) -> bool:
 
 
 class Block(Part):
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: FeedForward, arrangement: str = "pre_norm"):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], arrangement: str = "pre_norm"):
         if arrangement not in ARRANGEMENTS:
             raise ValueError(f"unknown block arrangement {arrangement!r}; known: {ARRANGEMENTS}")
         if arrangement == "pre_norm" and norm2 is None:
             raise ValueError("the pre_norm arrangement needs a second norm")
+        if ffn is None and arrangement != "out_norm":
+            raise ValueError(f"the {arrangement} arrangement needs a feed-forward")
+        if arrangement == "out_norm" and (ffn is None) != (norm2 is None):
+            raise ValueError("the out_norm arrangement has a second norm exactly when it has a feed-forward")
         self.norm1, self.mixer, self.norm2, self.ffn, self.arrangement = norm1, mixer, norm2, ffn, arrangement
 
     def _parts(self):
@@ -78,6 +87,10 @@ class Block(Part):
         ``entry_spec`` was offered to it as ``following``) the ``UnscaledNorm`` of the first norm.  Returns the
         stream and what this block leaves, in the same two forms."""
         rows = resid.shape[0]
+        if isinstance(delta, StreamCopy) and self.arrangement != "out_norm":
+            delta = None  # the block before left nothing to add
+        if self.arrangement == "out_norm":
+            return self._forward_out_norm(resid, delta, batch, cache, write_cache)
         if self.arrangement == "pre_norm":
             n1 = delta if isinstance(delta, UnscaledNorm) else self.norm1.add_forward(resid, delta)
             spec2 = self._spec(self.norm2) if _offers(self.mixer, "fuses_into_norm", rows) and _offers(self.ffn, "takes_unscaled", rows) else None
@@ -94,3 +107,20 @@ class Block(Part):
         m = self.ffn.forward(n, batch)
         self.norm1.rt.ops.add_into_residual(resid, a)
         return resid, m
+
+    def _forward_out_norm(self, resid, delta, batch, cache, write_cache):
+        ops, narrow = self.rt.ops, self.rt.dtype != torch.float32
+        if isinstance(delta, UnscaledNorm):
+            raise ValueError("an out_norm block cannot follow a block that folded this block's norm into its product")
+        if isinstance(delta, StreamCopy):
+            x = delta.rows
+        else:
+            if delta is not None:
+                ops.add_into_residual(resid, delta)
+            x = None
+        if x is None:
+            x = ops.round_rows(resid) if narrow else resid
+        x = self.norm1.add_normed(resid, self.mixer.forward(x, batch, cache, write_cache))
+        if self.ffn is not None:
+            x = self.norm2.add_normed(resid, self.ffn.forward(x if narrow else resid, batch))
+        return resid, StreamCopy(x if narrow else None)

@@ -19,19 +19,44 @@ class Linear(Part):
     capture_safe = True
     kernels_only = True
 
-    def __init__(self, sources: Sequence[Tuple[str, int]], in_features: int):
+    def __init__(self, sources: Sequence[Tuple[str, int]], in_features: int, *, side_by_side: bool = False,
+                 column_groups: Optional[Tuple[int, int, int]] = None):
+        """``side_by_side``: the sources [out, in_i] share the output axis and are laid next to each other along the
+        input axis (``in_features`` is then the common OUTPUT size and the numbers in ``sources`` are input sizes), so
+        that one product sums what each matrix makes of its share of the input columns.  ``column_groups`` =
+        (groups, used, padded): the input arrives as ``groups`` groups of ``padded`` columns of which the first
+        ``used`` are real (heads whose rows are narrower than the cache's); the stored matrix [out, groups * used]
+        gets zero columns at load."""
         self.sources: List[Tuple[str, int]] = list(sources)
-        self.in_features = in_features
-        self.out_features = sum(n for _, n in self.sources)
+        self.side_by_side = side_by_side
+        self.column_groups = column_groups
+        total = sum(n for _, n in self.sources)
+        if side_by_side:
+            self.out_features, self.in_features = in_features, total
+        else:
+            self.out_features, self.in_features = total, in_features
+        if column_groups is not None:
+            groups, used, padded = column_groups
+            if side_by_side or groups * used != in_features or padded < used:
+                raise ValueError(f"column groups {column_groups} do not fit {in_features} input columns")
+            self.in_features = groups * padded
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {name: WeightSpec((n, self.in_features), "linear") for name, n in self.sources}
+        if self.side_by_side:
+            return {name: WeightSpec((self.out_features, n), "linear") for name, n in self.sources}
+        stored_in = self.in_features if self.column_groups is None else self.column_groups[0] * self.column_groups[1]
+        return {name: WeightSpec((n, stored_in), "linear") for name, n in self.sources}
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
         parts = [weights.stored(name).to(device=rt.device, dtype=rt.dtype) for name, _ in self.sources]
-        stacked = parts[0].contiguous() if len(parts) == 1 else torch.cat(parts, dim=0)
+        stacked = parts[0].contiguous() if len(parts) == 1 else torch.cat(parts, dim=1 if self.side_by_side else 0).contiguous()
+        if self.column_groups is not None and self.column_groups[1] != self.column_groups[2]:
+            groups, used, padded = self.column_groups
+            wide = torch.zeros((stacked.shape[0], groups, padded), dtype=stacked.dtype, device=stacked.device)
+            wide[:, :, :used] = stacked.view(stacked.shape[0], groups, used)
+            stacked = wide.view(stacked.shape[0], groups * padded)
         # the tensor-core product streams weights fastest from its own box layout (``ops.TiledWeight``)
         self.weight = rt.ops.tile_weight(stacked) if self.on_tensor_cores() else stacked
 

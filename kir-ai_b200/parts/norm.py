@@ -37,6 +37,11 @@ class RMSNorm(Norm):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.rt.ops.add_rmsnorm(x, None, self.weight, self.eps, self.rt.dtype)
 
+    def add_normed(self, resid: torch.Tensor, y: torch.Tensor) -> Optional[torch.Tensor]:
+        if y.dtype != torch.float32:
+            y = y.float()
+        return self.rt.ops.norm_add(resid, y, self.weight, self.eps, None if self.rt.dtype == torch.float32 else self.rt.dtype)
+
     def fused_spec(self) -> Optional[FusedNormSpec]:
         # the tensor-core products read and write rows in 16-byte units; KIRAI_FUSE_NORMS=0 keeps every norm a
         # kernel of its own (for comparing the two paths)

@@ -1,6 +1,6 @@
 """The one registry from an architecture's name to its configuration class and model.
 
-``architectures[0]`` of config.json picks the entry.  An entry is a typed
+``architectures[0]`` of config.json (or its string ``architecture``) picks the entry.  An entry is a typed
 configuration class (``from_dict``/``to_dict``) and a function that turns a
 configuration into a ``ModelPlan``.  The reference dispatches on ``model_type``
 with an enum (crates/llm-models/src/native_text.rs:55-68); here another
@@ -33,11 +33,18 @@ def resolve(name: str) -> Tuple[type, Callable]:
     return _REGISTRY[name]
 
 
-def config_from_dict(raw: dict):
+def architecture_name(raw: dict) -> str:
+    """The name under which a config.json's model is registered: ``architectures[0]``, or the string ``architecture``."""
     architectures = raw.get("architectures") or []
-    if not architectures:
-        raise ConfigError.unsupported("model config missing architecture")
-    config_class, _ = resolve(architectures[0])
+    if architectures:
+        return architectures[0]
+    if isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
+    raise ConfigError.unsupported("model config missing architecture")
+
+
+def config_from_dict(raw: dict):
+    config_class, _ = resolve(architecture_name(raw))
     return config_class.from_dict(raw)
 
 
@@ -57,6 +64,10 @@ def _register_builtin() -> None:
     from .models.qwen3 import build_qwen3_plan
 
     register_architecture("Qwen3ForCausalLM", Qwen3Config, build_qwen3_plan, replace=True)
+    from .config.zoferax import ZoferaxConfig
+    from .models.zoferax import build_zoferax_plan
+
+    register_architecture(ZoferaxConfig.architecture, ZoferaxConfig, build_zoferax_plan, replace=True)
 
 
 _register_builtin()
