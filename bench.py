@@ -247,6 +247,181 @@ def decode_stamps(batch: int, context: int, layers: int) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# --workload designs: the Zoferax decoder beside the dense Qwen3 decoder at equal layer sizes
+DESIGN_SIZES = {
+    # name: width, heads, kv heads, key size, value size, experts, top, expert ff, vocab
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=64, experts=8, top=2, ff=1024, vocab=32000),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, experts=16, top=2, ff=1536, vocab=32000),
+}
+
+
+def design_configs(size: dict, layers: int):
+    """(Zoferax config.json, Qwen3 config.json) of one size: the same width, heads and layer count; the dense
+    feed-forward is as large as the experts that one token uses (3 I H = 2 top ff H)."""
+    mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["vdim"], "scale": size["dim"] ** -0.5}
+    mlp = {"kind": "moe", "expert": {"ff": size["ff"]}, "router": {"experts": size["experts"], "top": size["top"]}}
+    zoferax = {"architecture": "Zoferax", "width": size["width"], "vocab": size["vocab"], "embedding": {"scale": size["width"] ** 0.5},
+               "norm": {"eps": 1e-5}, "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": mlp} for _ in range(layers)]}
+    intermediate = -(-(2 * size["top"] * size["ff"]) // (3 * 128)) * 128
+    dense = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=size["width"], intermediate_size=intermediate,
+                 num_hidden_layers=layers, num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"],
+                 head_dim=size["dim"], vocab_size=size["vocab"], max_position_embeddings=40960, rms_norm_eps=1e-6,
+                 rope_theta=1000000.0, tie_word_embeddings=False)
+    return zoferax, dense
+
+
+def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: float, size: dict, design: str, peaks) -> list:
+    """One row per entry point of a step: time, the work the DESIGN asks for (not what the kernel chose to compute), and
+    that work over the time as a fraction of the measured peak (bytes over the copy bandwidth or flops over the bf16
+    rate, whichever is the greater)."""
+    import re
+
+    width, heads, kvh, dk = size["width"], size["heads"], size["kv_heads"], size["dim"]
+    dv = size["vdim"] if design == "zoferax" else dk
+    routed = size["experts"] * size["ff"]
+    rows = []
+    for name, (count, ms) in sorted(summary.items(), key=lambda item: -item[1][1]):
+        flops = bytes_ = 0.0
+        label = name
+        match = re.search(r"m=(\d+) n=(\d+) k=(\d+) form=(\d+)", name)
+        if match and "grouped" in name:
+            # rows sorted by expert: the design's work is tokens * top rows through one expert's matrices each
+            m, n, k, form = map(int, match.groups())
+            rows_used = tokens * size["top"]
+            flops = 2.0 * rows_used * n * k * count
+            bytes_ = (2.0 * rows_used * (k + n) + 2.0 * size["experts"] * n * k) * count
+            label += " (experts, rows sorted by expert)"
+        elif match:
+            m, n, k, form = map(int, match.groups())
+            flops, bytes_ = 2.0 * m * n * k, 2.0 * (m * k + n * k) + m * (n // 2 if form == 2 else n) * (4 if form in (1, 3) else 2)
+            if design == "zoferax" and routed in (n, k):  # the experts: a token needs top of them
+                share = size["top"] / size["experts"]
+                flops *= share
+                bytes_ = 2.0 * m * k * (share if k == routed else 1) + 2.0 * n * k * min(1.0, share * max(1, m)) + m * n * 2.0 * (share if n == routed else 2)
+                label += " (experts; work = the chosen experts')"
+            flops, bytes_ = flops * count, bytes_ * count
+        elif "attention" in name:
+            flops = 2.0 * heads * (dk + dv) * context_pairs * count
+            bytes_ = (2.0 * kvh * (dk + dv) * cache_rows + 2.0 * tokens * heads * (dk + dv)) * count
+        elif "qkv_wide_norm" in name:
+            cols = heads * dk + kvh * (dk + dv)
+            bytes_ = tokens * (4.0 * cols + 2.0 * cols) * count
+        elif "qk_norm_rope" in name:
+            bytes_ = tokens * 2.0 * (2 * (heads + kvh) * dk + 2 * kvh * dk) * count
+        elif "norm_add" in name:
+            bytes_ = tokens * width * 14.0 * count
+        elif "add_rmsnorm" in name:
+            bytes_ = tokens * width * 12.0 * count
+        elif "route_" in name:
+            bytes_ = tokens * size["top"] * width * 4.0 * count
+        elif "relu2_gate" in name:
+            bytes_ = tokens * routed * 4.0 * count
+        elif "router" in name:
+            bytes_ = (tokens * width * 2.0 + size["experts"] * width * 4.0) * count
+        elif "embedding" in name or "round_rows" in name:
+            bytes_ = tokens * width * 6.0 * count
+        seconds = ms / 1e3
+        frac = max(bytes_ / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12)) / seconds if seconds > 0 else 0.0
+        rows.append({"kernel": label, "launches": count, "ms": round(ms, 4), "frac_of_measured_peak": round(frac, 3),
+                     "bound": "flops" if flops / (peaks["bf16_tflops"] * 1e12) > bytes_ / (peaks["hbm_gbs"] * 1e9) else "bytes"})
+    return rows
+
+
+def compare_designs(args) -> int:
+    """Prefill and decode throughput of the Zoferax design and of the dense Qwen3 decoder at equal layer sizes, random
+    weights, and each step's time by entry point with its fraction of the measured peaks.  Prints one JSON line."""
+    import torch
+
+    import kirai_b200  # noqa: F401
+    from kirai_b200 import Engine, SamplingParams
+    from kirai_b200.csrc import ops
+    from kirai_b200.engine.batch import StepEntry
+    from kirai_b200.registry import config_from_dict
+
+    peaks, peak_source = load_peaks()
+    warmup, steps = max(3, args.warmup), max(1, args.steps)
+    T, R, context, layers = args.prefill_tokens, args.batch, args.context, (8 if args.layers == QWEN3_8B["num_hidden_layers"] else args.layers)
+    torch.cuda.set_device(0)
+    generator = torch.Generator().manual_seed(99)
+    clocks = ClockSampler()
+    clocks.start()
+    out = {}
+    for size_name in [s for s in args.sizes.split(",") if s]:
+        size = DESIGN_SIZES[size_name]
+        for design, raw in zip(("zoferax", "qwen3-dense"), design_configs(size, layers)):
+            vocab = size["vocab"]
+            engine = Engine(config=config_from_dict(raw), random_weights_seed=3, dtype="bfloat16", page_size=args.page_size,
+                            max_new_tokens=4 * (warmup + steps) + 64, max_prefill_tokens=T, max_concurrent_requests=R,
+                            max_cache_tokens=(2 * R + 2) * (context + 256))
+            runner = engine.runner
+
+            def prompt(n):
+                return torch.randint(0, vocab, (n,), generator=generator).tolist()
+
+            # prefill: one prompt of T tokens through the step function
+            times = []
+            for it in range(warmup + 5):
+                pages = runner.cache.open(("prefill", it))
+                tokens = prompt(T)
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                runner.step([StepEntry(pages, tokens, [T - 1])], check_errors=False)
+                stop.record()
+                torch.cuda.synchronize()
+                if it >= warmup:
+                    times.append(start.elapsed_time(stop))
+                runner.cache.close(pages)
+            prefill_ms = statistics.median(times)
+            pages = runner.cache.open(("prefill", "timed"))
+            with ops.launch_timer() as timer:
+                runner.step([StepEntry(pages, prompt(T), [T - 1])], check_errors=False)
+            prefill_kernels = _kernel_rows(timer.summary(), T, T * (T + 1) / 2.0, T, size, design.split("-")[0], peaks)
+            runner.cache.close(pages)
+            # decode: R requests at the context length; through Engine.step (captured steps, host tokens in and out)
+            params = SamplingParams(temperature=0.0, max_new_tokens=4 * (warmup + steps) + 64, ignore_eos=True)
+            requests = [engine.add_request(prompt(context), params) for _ in range(R)]
+            while any(r.pending > 1 or not r.output for r in requests):
+                engine.step()
+            for _ in range(warmup + 8):
+                engine.step()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                engine.step()
+            torch.cuda.synchronize()
+            decode_ms = (time.perf_counter() - t0) / steps * 1e3
+            engine.drain()
+            for r in requests:
+                engine.scheduler.abort(r)
+            # the same step's kernels one by one: an eager step of R single tokens on caches filled to the context
+            held = [runner.cache.open(("decode", i)) for i in range(R)]
+            for request in held:
+                runner.step([StepEntry(request, prompt(context), [])], check_errors=False)
+            runner.step([StepEntry(request, prompt(1), [0]) for request in held], check_errors=False)
+            with ops.launch_timer() as timer:
+                runner.step([StepEntry(request, prompt(1), [0]) for request in held], check_errors=False)
+            decode_kernels = _kernel_rows(timer.summary(), R, R * (context + 2.0), R * (context + 2.0), size, design.split("-")[0], peaks)
+            ops.check_device_errors(runner.rt.device)
+            out[f"{size_name}/{design}"] = {
+                "prefill_tokens_per_s": T / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
+                "decode_tokens_per_s": R / (decode_ms / 1e3), "decode_ms_per_step": decode_ms,
+                "captured_decode_steps": engine.counters.get("graph_steps", 0),
+                "prefill_kernels": prefill_kernels, "decode_kernels": decode_kernels,
+            }
+            del engine, runner, held, requests
+            torch.cuda.empty_cache()
+    line = {"metric": "prefill and decode tokens/s, Zoferax beside dense Qwen3 at equal layer sizes", "unit": "tokens/s", "n_gpus": 1,
+            "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic: uniform-random token ids, random weights (seed 3)",
+            "config": {"sizes": {k: DESIGN_SIZES[k] for k in args.sizes.split(",") if k}, "layers": layers, "prefill_tokens": T,
+                       "decode_batch": R, "context": context, "page_size": args.page_size, "peaks": peak_source,
+                       "l2": "every size's weights and cache exceed L2"},
+            "results": out, "clocks": clocks.stop()}
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -261,13 +436,16 @@ def main() -> int:
     parser.add_argument("--points", default="1,64", help="other decode batches to measure (comma separated, '' for none)")
     parser.add_argument("--no-check", action="store_true",
                         help="skip the check of the captured decode step against the step function before each timing")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b", "decode-stamps"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b", "decode-stamps", "designs"],
                         help="decode: the contract's measurement (default).  serving-4b: 64 requests with prompts of "
                              "128..4096 tokens, 512-token prefill portions mixed with decode, 256 new tokens each, greedy, "
                              "Qwen3-4B shape.  batch-32b: 16 requests of 8,064 prompt tokens, 128 new tokens at temperature 1, "
                              "Qwen3-32B shape.  Both run through Engine.generate and print their own one line.  decode-stamps: "
                              "the kernels' own clock stamps inside one captured decode step (--batch, --context, --layers; "
-                             "4 layers are enough), a table instead of the JSON line.")
+                             "4 layers are enough), a table instead of the JSON line.  designs: prefill and decode of the "
+                             "Zoferax decoder beside the dense Qwen3 decoder at equal layer sizes (--sizes), with every "
+                             "step's time by kernel; a line of its own.")
+    parser.add_argument("--sizes", default="2k,4k", help="layer sizes of --workload designs: " + ", ".join(DESIGN_SIZES))
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -279,6 +457,8 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.workload == "designs":
+        return compare_designs(args)
     if args.workload == "decode-stamps":
         return decode_stamps(args.batch, args.context, min(args.layers, 4) if args.layers == QWEN3_8B["num_hidden_layers"] else args.layers)
     if args.workload != "decode":

@@ -98,6 +98,7 @@ __host__ __device__ constexpr int tmem_columns() { return BN <= 32 ? 32 : (BN <=
 //    (0 when that variance is 0), which is what the product of the normed rows would have been.
 //  * EPI 2 (residual and next norm): residual[m][n] += product; C[m][n] = bf16(residual * norm_weight[n]) is the
 //    unscaled input of the next product, and sumsq_out[tile][m] receives this tile's share of sum_n residual^2.
+//  * EPI 3 (persistent kernel only): C = relu(product)^2.
 struct Epilogue {
     const float* row_sumsq;
     int row_parts;
@@ -106,6 +107,10 @@ struct Epilogue {
     const float* norm_weight;
     float* sumsq_out;
     unsigned long long* stamps;  // null, or [CTAs][8] clock stamps (ns) of the streaming kernel, for measurements
+    // Grouped products (persistent kernel only): W holds `groups` matrices [N, K] one after the other, and the 128 rows
+    // of A's tile m are multiplied with matrix tile_group[m] (rows of A sorted by group, every group's rows padded to
+    // whole tiles); a tile with a negative group holds no rows and is left out.  Null: one matrix.
+    const int* tile_group = nullptr;
 };
 
 // Clock stamps of one CTA of the streaming kernel, written only when a buffer is given: 0 the CTA starts, 1 the kernel
@@ -793,8 +798,17 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
             struct Cursor {
                 int t, kb, stage, m_tile, n_tile;
                 uint32_t round;  // how often the ring has wrapped
+                int group;       // which of W's matrices the tile's rows are multiplied with
             };
-            auto place = [&](Cursor& c) { c.m_tile = c.t % m_tiles, c.n_tile = c.t / m_tiles; };
+            const int* tile_group = ep.tile_group;
+            if (tile_group) pdl_wait();  // the kernel before may still be writing which tile belongs to which group
+            auto place = [&](Cursor& c) {
+                c.m_tile = c.t % m_tiles, c.n_tile = c.t / m_tiles, c.group = 0;
+                while (tile_group && c.t < total_tiles && (c.group = tile_group[c.m_tile]) < 0) {
+                    c.t += (int)gridDim.x;  // a tile without rows is left out by every role
+                    c.m_tile = c.t % m_tiles, c.n_tile = c.t / m_tiles;
+                }
+            };
             auto advance = [&](Cursor& c) {
                 if (++c.kb == num_kb) { c.kb = 0, c.t += (int)gridDim.x; place(c); }
                 if (++c.stage == STAGES) { c.stage = 0, ++c.round; }
@@ -809,19 +823,19 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                     const int first = c.n_tile * (BN / GEMM_BM);
                     const int boxes = min(BN / GEMM_BM, row_tiles - first);
                     mbar_expect_tx(full, Smem::x_bytes + boxes * GEMM_BOX_BYTES);
-                    const uint8_t* src = w_tiled + ((size_t)first * num_kb + c.kb) * GEMM_BOX_BYTES;
+                    const uint8_t* src = w_tiled + ((size_t)(first + c.group * row_tiles) * num_kb + c.kb) * GEMM_BOX_BYTES;
                     for (int b = 0; b < boxes; ++b)
                         bulk_load_1d(dst + Smem::x_bytes + b * GEMM_BOX_BYTES, src + (size_t)b * num_kb * GEMM_BOX_BYTES,
                                      GEMM_BOX_BYTES, full);
                 } else if (weights) {
                     mbar_expect_tx(full, Smem::stage_bytes);
-                    tma_load_2d(dst + Smem::x_bytes, &map_y, full, c.kb * GEMM_BK, c.n_tile * BN);
+                    tma_load_2d(dst + Smem::x_bytes, &map_y, full, c.kb * GEMM_BK, c.group * N + c.n_tile * BN);
                 }
                 if (activations) tma_load_2d(dst, &map_x, full, c.kb * GEMM_BK, c.m_tile * GEMM_BM);
             };
             // The weights do not depend on the kernel before this one: the first ring of weight tiles is
             // fetched at once, and only the activation tiles wait for that kernel to finish.
-            Cursor ahead{(int)blockIdx.x, 0, 0, 0, 0, 0u};
+            Cursor ahead{(int)blockIdx.x, 0, 0, 0, 0, 0u, 0};
             place(ahead);
             Cursor behind = ahead;
             int head = 0;
@@ -837,8 +851,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
     } else if (warp == 1) {
         if (elect_one()) {
             constexpr uint32_t idesc = instr_desc_bf16(GEMM_BM, BN);
-            int it = 0, local = 0;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+            int it = 0, handled = 0;
+            if (ep.tile_group) pdl_wait();
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                if (ep.tile_group && ep.tile_group[t % m_tiles] < 0) continue;
+                const int local = handled++;
                 const int buf = local & 1;
                 // the epilogue must have drained this accumulator (two tiles ago)
                 if (local >= 2 && !mbar_wait(smem_addr(&acc_empty[buf]), (uint32_t)((local >> 1) - 1) & 1u)) { ok = false; break; }
@@ -867,8 +884,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
         // whether the residual-and-norm epilogue can take its coalesced form (whole 16-byte pieces everywhere)
         const bool coalesced = EPI == 2 && N % 4 == 0 && ldc % 4 == 0 &&
                                (((uintptr_t)ep.residual | (uintptr_t)ep.norm_weight | (uintptr_t)C) & 15) == 0;
-        int local = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+        int handled = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            if (ep.tile_group && ep.tile_group[t % m_tiles] < 0) continue;
+            const int local = handled++;
             const int buf = local & 1;
             const int n_tile = t / m_tiles;
             const int x0 = (t % m_tiles) * GEMM_BM, y0 = n_tile * BN;
@@ -924,6 +943,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                 float v[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * my_scale;
+                if (EPI == 3) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = v[j] > 0.0f ? v[j] * v[j] : 0.0f;
+                }
                 if (EPI == 2) {
                     float* res = ep.residual + (size_t)x_row * N + y0 + c0;
                     OutT* dst = C + (size_t)x_row * ldc + y0 + c0;
@@ -1021,12 +1044,12 @@ static int sm_count() {
 }
 template <int BN, typename OutT, int EPI>
 static int launch_persistent(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
-                             const Epilogue& ep, int* error_flag, cudaStream_t stream) {
+                             const Epilogue& ep, int* error_flag, cudaStream_t stream, int groups = 1) {
     using Smem = GemmSmem<BN>;
     CUtensorMap map_a, map_w;
     if (!tmap::bf16_2d_sw128(&map_a, A, M, K, lda, GEMM_BM, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
     if (tiled) map_w = map_a;  // not read: the boxes are fetched by address
-    else if (!tmap::bf16_2d_sw128(&map_w, W, N, K, K, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
+    else if (!tmap::bf16_2d_sw128(&map_w, W, (uint64_t)N * groups, K, K, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
     if (tiled && ((uintptr_t)W & 15)) return KIRAI_ERR_BAD_ALIGN;
     const long tiles = (long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
     const int sms = sm_count();
@@ -1206,6 +1229,30 @@ KIRAI_EXPORT long kirai_gemm_bf16_tiled_bytes(int N, int K) {
 // gemm_stamp) to the next 8 * 1,024 words of it.  Null (the default) switches the stamps off.
 static unsigned long long* g_gemm_stamps = nullptr;
 KIRAI_EXPORT void kirai_gemm_bf16_set_stamps(unsigned long long* buffer) { g_gemm_stamps = buffer; }
+
+// A grouped product for rows sorted by group: A [M, K] (M a multiple of 128), W = `groups` matrices [N, K] one after the
+// other (row-major [groups * N, K]; or tiled, every matrix a whole number of 128-row boxes: N a multiple of 128),
+// tile_group [M / 128] (on the device) = the matrix of each 128-row tile of A.  C [M, N].
+//   form 0: bf16.  1: float.  4: bf16 relu(product)^2.
+KIRAI_EXPORT int kirai_gemm_bf16_grouped(const void* A, const void* W, int tiled, void* C, int M, int N, int K, long lda, long ldc,
+                                         int groups, const int* tile_group, int form, int* error_flag, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || groups <= 0 || !tile_group || M % GEMM_BM != 0) return KIRAI_ERR_BAD_SIZE;
+    if (K % 8 != 0 || lda % 8 != 0) return KIRAI_ERR_BAD_ALIGN;
+    if (tiled && N % GEMM_BM != 0) return KIRAI_ERR_BAD_SIZE;
+    Epilogue ep{nullptr, 0, 1.0f, 0.0f, nullptr, nullptr, nullptr, nullptr};
+    ep.tile_group = tile_group;
+#define KIRAI_GROUPED(OutT, EPI)                                                                                                  \
+    return N <= 128 ? launch_persistent<128, OutT, EPI>(A, W, tiled != 0, C, M, N, K, lda, ldc, ep, error_flag, stream, groups) \
+                    : launch_persistent<256, OutT, EPI>(A, W, tiled != 0, C, M, N, K, lda, ldc, ep, error_flag, stream, groups)
+    switch (form) {
+        case 0: KIRAI_GROUPED(bf16, 0);
+        case 1: KIRAI_GROUPED(float, 0);
+        case 4: KIRAI_GROUPED(bf16, 3);
+    }
+#undef KIRAI_GROUPED
+    return KIRAI_ERR_BAD_SIZE;
+}
 
 // The one entry point of the tensor-core product, A[M, K] (row stride lda) times W[N, K] transposed.
 //   tiled:  W is in the tiled form described at the top of this file, else row-major.

@@ -171,6 +171,19 @@ KIRAI_EXPORT int kirai_round_rows_bf16(const float* src, void* dst, long count, 
 // columns).  The cache is [pages, 2, nkv, page, dpad]; its columns beyond dk and dv are never written and stay zero
 // from creation.  A null bias adds nothing, a null norm weight leaves the rows unnormed.
 template <typename T>
+__device__ __forceinline__ void store4(T* dst, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename T, bool VEC>
 __global__ void qkv_wide_norm_write_kernel(const float* __restrict__ qkv, long qkv_stride, const float* __restrict__ q_bias,
                                            const float* __restrict__ k_bias, const float* __restrict__ v_bias,
                                            const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
@@ -198,13 +211,30 @@ __global__ void qkv_wide_norm_write_kernel(const float* __restrict__ qkv, long q
     pdl_wait();
     const float* src = qkv + (size_t)token * qkv_stride;
     float q_acc = 0.0f, k_acc = 0.0f;
-    for (int i = threadIdx.x; i < q_cols + k_cols; i += blockDim.x) {
-        const bool is_q = i < q_cols;
-        const float* bias = is_q ? q_bias : k_bias;
-        const float v = src[i] + (bias ? bias[is_q ? i : i - q_cols] : 0.0f);
-        row_s[i] = v;
-        if (is_q) q_acc = fmaf(v, v, q_acc);
-        else k_acc = fmaf(v, v, k_acc);
+    if (VEC) {
+        // four columns at a time (every width and pointer allows 16-byte loads; see the launch)
+        for (int i = threadIdx.x * 4; i < q_cols + k_cols; i += blockDim.x * 4) {
+            const bool is_q = i < q_cols;
+            const float* bias = is_q ? q_bias : k_bias;
+            float4 v = *reinterpret_cast<const float4*>(src + i);
+            if (bias) {
+                const float4 b = *reinterpret_cast<const float4*>(bias + (is_q ? i : i - q_cols));
+                v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+            }
+            *reinterpret_cast<float4*>(row_s + i) = v;
+            const float sq = (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+            if (is_q) q_acc += sq;
+            else k_acc += sq;
+        }
+    } else {
+        for (int i = threadIdx.x; i < q_cols + k_cols; i += blockDim.x) {
+            const bool is_q = i < q_cols;
+            const float* bias = is_q ? q_bias : k_bias;
+            const float v = src[i] + (bias ? bias[is_q ? i : i - q_cols] : 0.0f);
+            row_s[i] = v;
+            if (is_q) q_acc = fmaf(v, v, q_acc);
+            else k_acc = fmaf(v, v, k_acc);
+        }
     }
     const float q_total = block_sum(q_acc, scratch);
     const float k_total = kv_heads > 0 ? block_sum(k_acc, scratch) : 0.0f;
@@ -219,6 +249,38 @@ __global__ void qkv_wide_norm_write_kernel(const float* __restrict__ qkv, long q
         k_scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
     }
     T* q_dst = q_out + (size_t)token * q_heads * dpad;
+    const long head_rows = (long)page_size * dpad;  // from one kv head's rows of a page to the next head's
+    const long value_base = page_base + (long)kv_heads * head_rows;
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < q_heads * dpad; i += blockDim.x * 4) {
+            const int head = i / dpad, c = i - head * dpad;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (c < dk) {
+                const int col = head * dk + c;
+                v = *reinterpret_cast<const float4*>(row_s + col);
+                const float4 w = q_weight ? *reinterpret_cast<const float4*>(q_weight + col) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                v.x *= q_scale * w.x, v.y *= q_scale * w.y, v.z *= q_scale * w.z, v.w *= q_scale * w.w;
+            }
+            store4<T>(q_dst + i, v);
+        }
+        if (page_base < 0) return;
+        for (int i = threadIdx.x * 4; i < k_cols; i += blockDim.x * 4) {
+            const int head = i / dk, c = i - head * dk;
+            float4 v = *reinterpret_cast<const float4*>(row_s + q_cols + i);
+            const float4 w = k_weight ? *reinterpret_cast<const float4*>(k_weight + i) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            v.x *= k_scale * w.x, v.y *= k_scale * w.y, v.z *= k_scale * w.z, v.w *= k_scale * w.w;
+            store4<T>(cache + page_base + head * head_rows + c, v);
+        }
+        for (int i = threadIdx.x * 4; i < v_cols; i += blockDim.x * 4) {
+            const int head = i / dv, c = i - head * dv;
+            float4 v = *reinterpret_cast<const float4*>(src + q_cols + k_cols + i);
+            if (v_bias) {
+                const float4 b = *reinterpret_cast<const float4*>(v_bias + i);
+                v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+            }
+            store4<T>(cache + value_base + head * head_rows + c, v);
+        }
+    } else {
     for (int i = threadIdx.x; i < q_heads * dpad; i += blockDim.x) {
         const int head = i / dpad, c = i - head * dpad;
         float v = 0.0f;
@@ -229,16 +291,15 @@ __global__ void qkv_wide_norm_write_kernel(const float* __restrict__ qkv, long q
         q_dst[i] = from_f32<T>(v);
     }
     if (page_base < 0) return;
-    const long head_rows = (long)page_size * dpad;  // from one kv head's rows of a page to the next head's
     for (int i = threadIdx.x; i < k_cols; i += blockDim.x) {
         const int head = i / dk, c = i - head * dk;
         cache[page_base + head * head_rows + c] = from_f32<T>(row_s[q_cols + i] * k_scale * (k_weight ? k_weight[i] : 1.0f));
     }
-    const long value_base = page_base + (long)kv_heads * head_rows;
     for (int i = threadIdx.x; i < v_cols; i += blockDim.x) {
         const int head = i / dv, c = i - head * dv;
         const float v = src[q_cols + k_cols + i] + (v_bias ? v_bias[i] : 0.0f);
         cache[value_base + head * head_rows + c] = from_f32<T>(v);
+    }
     }
 }
 
@@ -253,7 +314,11 @@ static int qkv_wide_norm_write_launch(const float* qkv, long qkv_stride, const f
     if (kv_heads > 0 && !cache) return KIRAI_ERR_BAD_SIZE;
     const size_t smem = (size_t)(q_heads + kv_heads) * dk * sizeof(float);
     if (smem > 200 * 1024) return KIRAI_ERR_BAD_SIZE;
-    auto kernel = qkv_wide_norm_write_kernel<T>;
+    // four columns at a time where every width, stride and pointer is a multiple of four values
+    const bool vec = dk % 4 == 0 && dv % 4 == 0 && dpad % 4 == 0 && qkv_stride % 4 == 0 &&
+                     (((uintptr_t)qkv | (uintptr_t)q_bias | (uintptr_t)k_bias | (uintptr_t)v_bias | (uintptr_t)q_weight |
+                       (uintptr_t)k_weight | (uintptr_t)q_out | (uintptr_t)cache) & 15) == 0;
+    auto kernel = vec ? qkv_wide_norm_write_kernel<T, true> : qkv_wide_norm_write_kernel<T, false>;
     if (smem > 48 * 1024) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;

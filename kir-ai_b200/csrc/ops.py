@@ -92,21 +92,59 @@ launch_count = 0  # entry points called so far (each launches one to three kerne
 launch_counts: dict = {}  # the same by entry point: which kernels a step used, and how often (Engine.stats reports it)
 
 
-def _call(name: str, *args) -> None:
+def _call(name: str, *args, detail: str = "") -> None:
     """Launches one entry point on the current stream.  Products that were held back to be launched together
     (see ``chained_products``) go first: launches keep the order in which they were asked for."""
     if _pending:
         flush_products()
-    _launch(name, *args)
+    _launch(name, *args, detail=detail)
 
 
-def _launch(name: str, *args) -> None:
+def _launch(name: str, *args, detail: str = "") -> None:
     global launch_count
     fn = getattr(library(), name)
     fn.restype = ctypes.c_int
-    _check(fn(*args), name)
+    if _timer is not None:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        _check(fn(*args), name)
+        stop.record()
+        _timer.records.append((name + detail, start, stop))
+    else:
+        _check(fn(*args), name)
     launch_count += 1
     launch_counts[name] = launch_counts.get(name, 0) + 1
+
+
+_timer = None
+
+
+class launch_timer:
+    """``with ops.launch_timer() as timer: ...`` brackets every entry point launched inside with CUDA events on the
+    current stream; ``timer.summary()`` (which waits for the device) gives {entry point (products with their sizes):
+    (launches, total ms)}.  For measurements only: the events keep a kernel from starting beside the end of the one
+    before it, so a step takes longer under the timer than without."""
+
+    def __init__(self):
+        self.records = []
+
+    def __enter__(self):
+        global _timer
+        _timer = self
+        return self
+
+    def __exit__(self, kind, value, traceback):
+        global _timer
+        _timer = None
+        return False
+
+    def summary(self) -> dict:
+        torch.cuda.synchronize()
+        out: dict = {}
+        for name, start, stop in self.records:
+            count, total = out.get(name, (0, 0.0))
+            out[name] = (count + 1, total + start.elapsed_time(stop))
+        return out
 
 
 _i = ctypes.c_int
@@ -309,6 +347,24 @@ def qkv_wide_norm_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim:
     return q_out
 
 
+_arrival_counters: dict = {}
+
+
+def _router_arrivals(device: torch.device, tokens: int) -> torch.Tensor:
+    """The router kernel's counters, one per token: zero between launches (the kernel sets them back), one buffer per
+    device that grows with the largest step seen.  Launches on one device run one after the other, as a step's do."""
+    key = torch.device(device)
+    if key.index is None:
+        key = torch.device("cuda", torch.cuda.current_device())
+    counters = _arrival_counters.get(key)
+    if counters is None or counters.numel() < tokens:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the router's counters must exist before a stream capture begins: run the step once outside the capture")
+        counters = torch.zeros(max(4096, 2 * tokens), dtype=torch.int32, device=key)
+        _arrival_counters[key] = counters
+    return counters
+
+
 def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: bool = False):
     """Routing weights of every token: logits ``router`` [experts, H] (float32) times ``x`` [T, H] in 32-bit, the ``top``
     largest chosen (the lower index on a tie), softmax over the chosen logits alone.  Returns gates [T, experts]
@@ -322,8 +378,20 @@ def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: b
     ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device) if want_chosen else None
     weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device) if want_chosen else None
     _call(f"kirai_router_gates_{_suffix(x.dtype)}", _ptr(x), _l(x.stride(0)), _ptr(router), _ptr(gates), _ptr(ids), _ptr(weights),
-          _i(tokens), _i(x.shape[1]), _i(experts), _i(top), _stream())
+          _ptr(_router_arrivals(x.device, tokens)), _i(tokens), _i(x.shape[1]), _i(experts), _i(top), _stream())
     return (gates, ids, weights) if want_chosen else gates
+
+
+def router_choose_(logits: torch.Tensor, top: int, want_chosen: bool = False):
+    """The choice alone: ``logits`` [T, experts] (float32, as a product left them) become the routing weights in place
+    (see ``router_gates``).  Returns what ``router_gates`` returns."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous() and 0 < top <= logits.shape[1]
+    tokens, experts = logits.shape
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=logits.device) if want_chosen else None
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device) if want_chosen else None
+    _call("kirai_router_choose", _ptr(logits), _ptr(ids), _ptr(weights), _i(tokens), _i(experts), _i(top), _stream())
+    return (logits, ids, weights) if want_chosen else logits
 
 
 def relu2_gate_(up: torch.Tensor, gates: torch.Tensor, ff: int) -> torch.Tensor:
@@ -334,6 +402,68 @@ def relu2_gate_(up: torch.Tensor, gates: torch.Tensor, ff: int) -> torch.Tensor:
     assert up.shape == (gates.shape[0], experts * ff)
     _call(f"kirai_relu2_gate_{_suffix(up.dtype)}", _ptr(up), _ptr(gates), _i(up.shape[0]), _i(experts), _i(ff), _stream())
     return up
+
+
+def grouped_rows_capacity(tokens: int, top: int, experts: int) -> int:
+    """Tiles of 128 rows that always hold ``tokens * top`` rows sorted by expert, every expert's stretch padded to whole tiles."""
+    return (tokens * top + experts * 127 + 127) // 128
+
+
+def route_plan(chosen_ids: torch.Tensor, experts: int):
+    """Lays the (token, chosen expert) pairs of ``chosen_ids`` [T, top] (int32) out as rows sorted by expert, each
+    expert's stretch padded to whole tiles of 128 rows.  Returns (tile_group [tiles] = the expert of each tile, slot_of
+    [T, top] = the row of each pair, row_of_slot [tiles * 128] = the token of each row, -1 for padding)."""
+    _need_cuda(chosen_ids)
+    assert chosen_ids.dtype == torch.int32 and chosen_ids.dim() == 2 and chosen_ids.is_contiguous()
+    tokens, top = chosen_ids.shape
+    tiles = grouped_rows_capacity(tokens, top, experts)
+    tile_group = torch.empty(tiles, dtype=torch.int32, device=chosen_ids.device)
+    slot_of = torch.empty((tokens, top), dtype=torch.int32, device=chosen_ids.device)
+    row_of_slot = torch.empty(tiles * 128, dtype=torch.int32, device=chosen_ids.device)
+    _call("kirai_route_plan", _ptr(chosen_ids), _ptr(tile_group), _ptr(slot_of), _ptr(row_of_slot), _i(tokens), _i(top),
+          _i(experts), _i(tiles), _stream())
+    return tile_group, slot_of, row_of_slot
+
+
+def route_gather(x: torch.Tensor, row_of_slot: torch.Tensor) -> torch.Tensor:
+    """sorted[slot] = x[row_of_slot[slot]] (zeros where the slot is padding); ``x`` [T, H] bfloat16."""
+    _need_cuda(x, row_of_slot)
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and row_of_slot.dtype == torch.int32
+    out = torch.empty((row_of_slot.numel(), x.shape[1]), dtype=torch.bfloat16, device=x.device)
+    _call("kirai_route_gather_bf16", _ptr(x), _l(x.stride(0)), _ptr(row_of_slot), _ptr(out), _i(row_of_slot.numel()),
+          _i(x.shape[1]), _stream())
+    return out
+
+
+def route_combine(y: torch.Tensor, slot_of: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * y[slot_of[t, j]] in 32-bit; ``y`` [slots, H]."""
+    _need_cuda(y, slot_of, weights)
+    assert y.dim() == 2 and y.is_contiguous() and slot_of.dtype == torch.int32 and slot_of.is_contiguous()
+    assert weights.dtype == torch.float32 and weights.shape == slot_of.shape and weights.is_contiguous()
+    tokens, top = slot_of.shape
+    out = torch.empty((tokens, y.shape[1]), dtype=torch.float32, device=y.device)
+    _call(f"kirai_route_combine_{_suffix(y.dtype)}", _ptr(y), _ptr(slot_of), _ptr(weights), _ptr(out), _i(tokens), _i(y.shape[1]),
+          _i(top), _stream())
+    return out
+
+
+def linear_grouped(x: torch.Tensor, weight, groups: int, tile_group: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                   relu2: bool = False) -> torch.Tensor:
+    """Rows sorted by group times one of ``groups`` stacked matrices each: ``x`` [tiles * 128, K] (bfloat16), ``weight``
+    [groups * N, K] (row-major, or a ``TiledWeight`` with N a multiple of 128), ``tile_group`` [tiles] the matrix of each
+    128-row tile.  Returns [tiles * 128, N]; with ``relu2`` relu(product)^2 (bfloat16)."""
+    m, k, total = _check_product(x, weight)
+    _need_cuda(tile_group)
+    assert total % groups == 0 and m % 128 == 0 and tile_group.dtype == torch.int32 and tile_group.numel() == m // 128
+    n = total // groups
+    tiled = isinstance(weight, TiledWeight)
+    assert not relu2 or out_dtype == torch.bfloat16
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    form = 4 if relu2 else (0 if out_dtype == torch.bfloat16 else 1)
+    _call("kirai_gemm_bf16_grouped", _ptr(x), _ptr(weight.boxes if tiled else weight), _i(tiled), _ptr(out), _i(m), _i(n), _i(k),
+          _l(x.stride(0)), _l(n), _i(groups), _ptr(tile_group), _i(form), _ptr(error_flag(x.device)), _stream(),
+          detail=f" m={m} n={n} k={k} form={form}" if _timer is not None else "")
+    return out
 
 
 # ------------------------------------------------------------------- cache write
@@ -843,7 +973,8 @@ def _launch_product(item) -> None:
         scale_args = (_ptr(None), _i(0), _f(1.0), _f(0.0))
     _launch("kirai_gemm_bf16_general", _ptr(x), _ptr(weight.boxes if tiled else weight), _i(tiled), _ptr(out), _i(x.shape[0]),
             _i(n), _i(k), _l(x.stride(0)), _l(width), _i(splits), _i(form), *scale_args,
-            _ptr(resid), _ptr(norm_weight), _ptr(sumsq_out), _ptr(error_flag(x.device)), _stream())
+            _ptr(resid), _ptr(norm_weight), _ptr(sumsq_out), _ptr(error_flag(x.device)), _stream(),
+            detail=f" m={x.shape[0]} n={n} k={k} form={form}" if _timer is not None else "")
 
 
 def flush_products() -> None:

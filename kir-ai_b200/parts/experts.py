@@ -13,7 +13,19 @@ an expert that was not chosen), and the down product then sums the chosen
 experts' outputs in its own accumulation.  Nothing depends on how many tokens
 an expert drew, so a step of single tokens can be captured in a graph; the
 price is that every expert's rows are computed for every token, experts / top
-times the arithmetic that the chosen experts alone would need.
+times the arithmetic that the chosen experts alone would need.  For a step of
+few tokens that price is none: the products are bound by reading the weights,
+and a handful of tokens between them choose most experts anyway.
+
+Steps of many tokens (``GROUPED_MIN_ROWS`` pairs of token and chosen expert, in
+bfloat16, expert and model width multiples of 128) sort their pairs by expert
+on the device instead: a plan kernel gives every pair a row in a buffer whose
+experts' stretches are padded to tiles of 128 rows, the rows are gathered, two
+grouped products (the first with relu^2 in its epilogue) multiply every tile
+with its expert's matrices, and a combine kernel sums each token's rows with
+its routing weights in 32-bit.  Only the chosen experts' arithmetic is done.
+This path keeps a second copy of the down matrices, stacked along the output
+axis.  Neither path waits for the host.
 """
 from __future__ import annotations
 
@@ -25,6 +37,7 @@ from .base import FeedForward, Runtime, WeightSpec
 from .linear import Linear
 
 ACTIVATIONS = ("relu2",)
+GROUPED_MIN_ROWS = 512  # pairs of (token, chosen expert) from which a step sorts them by expert
 
 
 class RoutedExperts(FeedForward):
@@ -47,7 +60,10 @@ class RoutedExperts(FeedForward):
         self.up = Linear([(prefix + n["up"].format(e=e), expert_size) for e in range(experts)], hidden_size)
         self.down = Linear([(prefix + n["down"].format(e=e), expert_size) for e in range(experts)], hidden_size,
                            side_by_side=True)
+        self.down_stacked = Linear([(prefix + n["down"].format(e=e), hidden_size) for e in range(experts)], expert_size)
         self.router: Optional[torch.Tensor] = None
+        self.router_product: Optional[Linear] = None
+        self.grouped = False
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {self.router_name: WeightSpec((self.experts, self.hidden_size), "linear"),
@@ -58,10 +74,36 @@ class RoutedExperts(FeedForward):
         self.router = weights.on_device(self.router_name, torch.float32)
         self.up.load(weights, rt)
         self.down.load(weights, rt)
+        # sorting by expert pays only where a token uses a part of the experts, and needs whole 128-row boxes per expert
+        self.grouped = (rt.dtype == torch.bfloat16 and self.top < self.experts and self.expert_size % 128 == 0
+                        and self.hidden_size % 128 == 0 and hasattr(rt.ops, "linear_grouped"))
+        if self.grouped:
+            self.down_stacked.load(weights, rt)
+        # A router stored in bfloat16 times bfloat16 rows with 32-bit accumulation IS the 32-bit product of those
+        # values, so steps of many tokens take the tensor-core product for the logits and a kernel for the choice alone.
+        if rt.dtype == torch.bfloat16 and weights.stored(self.router_name).dtype == torch.bfloat16 and self.hidden_size % 8 == 0:
+            self.router_product = Linear([(self.router_name, self.experts)], self.hidden_size)
+            self.router_product.load(weights, rt)
+
+    ROUTER_PRODUCT_MIN_ROWS = 128
+
+    def _route(self, x: torch.Tensor, want_chosen: bool):
+        ops = self.rt.ops
+        if self.router_product is not None and x.shape[0] >= self.ROUTER_PRODUCT_MIN_ROWS:
+            return ops.router_choose_(self.router_product.forward(x, torch.float32), self.top, want_chosen)
+        return ops.router_gates(x, self.router, self.top, want_chosen)
 
     def forward(self, x: torch.Tensor, batch=None) -> torch.Tensor:
         ops = self.rt.ops
-        gates = ops.router_gates(x, self.router, self.top)
+        if self.grouped and x.shape[0] * self.top >= GROUPED_MIN_ROWS:
+            _, ids, mix = self._route(x, True)
+            tile_group, slot_of, row_of_slot = ops.route_plan(ids, self.experts)
+            rows = ops.route_gather(x, row_of_slot)
+            hidden = ops.linear_grouped(rows, self.up.weight, self.experts, tile_group, relu2=True)
+            y = ops.linear_grouped(hidden, self.down_stacked.weight, self.experts, tile_group)
+            out = ops.route_combine(y, slot_of, mix)
+            return out if self.out_dtype == torch.float32 else ops.round_rows(out)
+        gates = self._route(x, False)
         hidden = self.up.forward(x)
         ops.relu2_gate_(hidden, gates, self.expert_size)
         return self.down.forward(hidden, self.out_dtype)

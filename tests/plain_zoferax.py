@@ -77,10 +77,21 @@ def relu_squared(z: torch.Tensor) -> torch.Tensor:
     return torch.relu(z) ** 2
 
 
-def routed_experts(x, weights, prefix: str, experts: int, top: int) -> torch.Tensor:
+def router_margins(logits: torch.Tensor, top: int) -> torch.Tensor:
+    """How far each row is from another choice of experts: the gap between the last chosen logit and the first one left
+    out, relative to the row's largest logit in size (infinite when every expert is chosen)."""
+    if top >= logits.shape[-1]:
+        return torch.full(logits.shape[:-1], float("inf"))
+    ordered = torch.sort(logits, dim=-1, descending=True).values
+    return (ordered[..., top - 1] - ordered[..., top]) / logits.abs().max(dim=-1).values.clamp_min(1e-30)
+
+
+def routed_experts(x, weights, prefix: str, experts: int, top: int, margins=None) -> torch.Tensor:
     """Each row goes through its ``top`` experts with the largest router logits; their outputs are mixed with
-    the softmax over those chosen logits alone."""
+    the softmax over those chosen logits alone.  ``margins`` (a list) receives this call's ``router_margins``."""
     logits = projection(x, weights[prefix + "router"])
+    if margins is not None:
+        margins.append(router_margins(logits, top))
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
         chosen = torch.topk(logits[t], top).indices
@@ -91,8 +102,9 @@ def routed_experts(x, weights, prefix: str, experts: int, top: int) -> torch.Ten
     return out
 
 
-def forward(config: dict, weights: dict, tokens, keep_layers: bool = False):
-    """Logits [T, vocab] of one whole sequence (and, with ``keep_layers``, the stream after every layer)."""
+def forward(config: dict, weights: dict, tokens, keep_layers: bool = False, margins=None):
+    """Logits [T, vocab] of one whole sequence (and, with ``keep_layers``, the stream after every layer).  ``margins``
+    (a list) receives one tensor [T] of router margins per layer with experts."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     E, eps = config["width"], config["norm"]["eps"]
     x = scaled_embedding(weights["embed"], tokens, config["embedding"]["scale"])
@@ -110,7 +122,7 @@ def forward(config: dict, weights: dict, tokens, keep_layers: bool = False):
         if mlp is not None:
             if mlp["kind"] != "moe":
                 raise ValueError(f"unknown feed-forward kind {mlp['kind']!r}")
-            y = routed_experts(x, weights, base + "mlp.", mlp["router"]["experts"], mlp["router"]["top"])
+            y = routed_experts(x, weights, base + "mlp.", mlp["router"]["experts"], mlp["router"]["top"], margins)
             x = x + rms_unit(y, eps) * weights[base + "norm2"].float()
         streams.append(x.clone())
     logits = projection(rms_unit(x, eps) * weights["final.norm"].float(), weights["head"])
