@@ -180,7 +180,7 @@ def _expert_tensors(part, seed):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("count,top,ff,width", [(8, 2, 16, 64), (3, 1, 20, 100), (3, 3, 12, 36), (40, 5, 8, 24), (1, 1, 8, 16)])
+@pytest.mark.parametrize("count,top,ff,width", [(8, 2, 16, 64), (3, 1, 20, 100), (3, 3, 12, 36), (40, 5, 8, 24), (1, 1, 8, 16), (3, 2, 10, 30)])
 def test_routed_experts(dtype, count, top, ff, width):
     from part_helpers import DEV, load_part
     from kirai_b200.parts import RoutedExperts
@@ -238,8 +238,9 @@ def _attention_part(mixer, width, shares=False):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("mixer,width,page", [(attention(4, 2, 16, 8, 2.0), 64, 4), (attention(6, 1, 12, 20, 1.5), 100, 8),
-                                              (attention(3, 3, 20, 4, 3.0), 40, 16), (attention(2, 1, 64, 64, 0.7), 32, 2)])
+@pytest.mark.parametrize("mixer,width,page", [(attention(4, 2, 16, 8, 0.8), 64, 4), (attention(6, 1, 12, 20, 0.9), 100, 8),
+                                              (attention(3, 3, 20, 4, 0.6), 40, 16), (attention(2, 1, 64, 64, 0.2), 32, 2),
+                                              (attention(2, 1, 10, 6, 1.0), 30, 16), (attention(40, 2, 8, 8, 1.0), 64, 32)])
 def test_attention_part_whole_in_portions_and_one_by_one(dtype, mixer, width, page):
     """One attention layer over 150 tokens: whole, in uneven portions, and token by token, against the plain function;
     then a second request on pages that the first gave back."""
@@ -499,6 +500,50 @@ def test_bounds_would_show_a_lost_key_or_a_wrong_expert(tiny):
     finally:
         plain.routed_experts = original_router
     assert float(np.abs(other - true).max()) > 3 * bound
+
+
+# R: sizes at which steps of many tokens sort their rows by expert and take the router's tensor-core product (width and
+# expert size multiples of 128), with a sharing layer.
+CONFIG_R = {
+    "architecture": "Zoferax", "width": 128, "vocab": 160, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5},
+    "layers": [
+        layer(attention(2, 1, 32, 16, 0.3), experts(4, 2, 128)),
+        layer(attention(2, 1, 32, 16, 0.3, kv_from=0), experts(6, 1, 128)),
+    ],
+}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_many_tokens_sort_rows_by_expert(dtype, tmp_path):
+    """A prompt of 400 tokens in one step (800 and 400 pairs of token and expert: the first layer sorts them, in
+    bfloat16), then in portions that stay below the threshold, then a mixed step in which a long portion rides beside
+    decoded tokens of another request: the same logits every way."""
+    from replay_client import Replay
+    from kirai_b200.csrc import ops
+
+    folder = str(tmp_path / "model")
+    write_model(folder, CONFIG_R, 6)
+    config, weights = read_model_folder(folder)
+    long_tokens, short_tokens = random_tokens(400, 160, 31), random_tokens(40, 160, 32)
+    reference = {"long": reference_with_close_calls(config, weights, long_tokens),
+                 "short": reference_with_close_calls(config, weights, short_tokens)}
+    assert reference["long"].close.mean() <= 0.4
+    replay = Replay(folder, dtype, str(tmp_path / "out"), max_tokens=480, page_size=16)
+    got = replay.step([("long", long_tokens, range(400))], end=["long"])
+    check(dtype, got, reference["long"], list(range(400)), "whole")
+    start = 0
+    for size in (130, 7, 130, 133):
+        got = replay.step([("again", long_tokens[start : start + size], range(size))])
+        check(dtype, got, reference["long"], list(range(start, start + size)), f"portion at {start}+{size}")
+        start += size
+    replay.step([], end=["again"])
+    got = replay.step([("short", short_tokens[:30], [29])])
+    check(dtype, got, reference["short"], [29], "short prompt")
+    got = replay.step([("short", [short_tokens[30]], [0]), ("third", long_tokens[:300], range(300))])
+    check(dtype, got[:1], reference["short"], [30], "decoded beside a long portion")
+    check(dtype, got[1:], reference["long"], list(range(300)), "long portion beside a decoded token")
+    assert replay.close() == 0
 
 
 def _margin_ok(config, weights, prompt, generated):
