@@ -118,13 +118,16 @@ class DecoderModel:
         """The residual stream [T, H] (32-bit) and the last block's not-yet-added output."""
         nvtx = torch.cuda.nvtx if self.nvtx else None  # ranges around the layer calls, for a timeline tool
         with self.rt.ops.chained_products(self._kernels_only):
-            embedding = self.plan.embedding
-            if getattr(embedding, "uses_positions", False):
+            embedding, order, delta = self.plan.embedding, self.plan.order, None
+            first = self.plan.blocks[order[0].block] if order else None
+            if getattr(first, "reads_stream", False) and hasattr(embedding, "forward_with_copy"):
+                # the first block reads the stream itself: its runtime-dtype copy is written with it
+                resid, copy = embedding.forward_with_copy(batch.token_ids, batch.positions)
+                delta = StreamCopy(copy) if copy is not None else None
+            elif getattr(embedding, "uses_positions", False):
                 resid = embedding.forward(batch.token_ids, batch.positions)
             else:
                 resid = embedding.forward(batch.token_ids)
-            delta = None
-            order = self.plan.order
             for i, call in enumerate(order):
                 view = cache.layer_view(call.cache) if call.cache is not None else None
                 following = self.plan.blocks[order[i + 1].block] if i + 1 < len(order) else None

@@ -26,7 +26,8 @@ class WeightSpec:
     """Shape and role of one named tensor.  The role tells the random-weights
     mode how to fill it and the loader which dtype family it must have:
     ``linear`` and ``embedding`` are floating matrices, ``norm`` a floating
-    vector, ``int_table`` an integer table (kept as int32)."""
+    vector around one, ``bias`` a floating vector around zero, ``int_table`` an
+    integer table (kept as int32)."""
 
     shape: Tuple[int, ...]
     role: str = "linear"

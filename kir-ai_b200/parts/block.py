@@ -51,6 +51,12 @@ class Block(Part):
         return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
     @property
+    def reads_stream(self) -> bool:
+        """Whether the block's first sub-layer reads the stream itself (rounded to the runtime dtype) and not a norm
+        of it: whoever made the stream may then hand its runtime-dtype copy along as a ``StreamCopy``."""
+        return self.arrangement == "out_norm"
+
+    @property
     def capture_safe(self) -> bool:
         return all(bool(getattr(part, "capture_safe", False)) for part in self._parts())
 

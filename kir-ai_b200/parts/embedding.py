@@ -68,6 +68,14 @@ class Embedding(Part):
         stream, _ = self.rt.ops.embedding_scaled(self.table, token_ids, self.scale, positions, self.frequencies)
         return stream
 
+    def forward_with_copy(self, token_ids: torch.Tensor, positions: Optional[torch.Tensor] = None):
+        """(stream, its copy in the runtime dtype or None when that is 32-bit): for a first block that reads the stream
+        itself, written in the same pass."""
+        if self.plain:
+            return self.forward(token_ids), None
+        return self.rt.ops.embedding_scaled(self.table, token_ids, self.scale, positions, self.frequencies,
+                                            copy_dtype=None if self.rt.dtype == torch.float32 else self.rt.dtype)
+
 
 class OutputHead(Part):
     """Logits = W x in 32-bit, W [V, H] (its own tensor, or the embedding table when tied)."""
