@@ -403,3 +403,72 @@ KIRAI_EXPORT int kirai_route_combine_f32(const void* y, const int* slot_of, cons
     return launch_pdl(route_combine_kernel<float>, dim3(tokens), dim3(hidden >= 2048 ? 256 : 128), 0, stream, 1u, (const float*)y,
                       slot_of, weights, out, hidden, top);
 }
+
+// route_combine and the norm on the feed-forward's output in one pass: row t of the experts' result is
+// sum_j weight[t, j] * y[slot_of[t, j]] in 32-bit (never written out), and stream[t] += row * rsqrt(mean(row^2) + eps) *
+// norm_weight; copy[t] = bf16(stream[t]).  One block per token, the row in registers (width a multiple of 4, at most
+// 4 * VEC * blockDim values).
+template <int VEC>
+__global__ void route_combine_norm_add_kernel(float* __restrict__ resid, const bf16* __restrict__ y, const int* __restrict__ slot_of,
+                                              const float* __restrict__ weights, const float* __restrict__ norm_weight,
+                                              bf16* __restrict__ copy, int hidden, int top, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int token = blockIdx.x;
+    const int quads = hidden >> 2;
+    float4 kept[VEC];
+    float acc = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        kept[n] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < quads) {
+            for (int j = 0; j < top; ++j) {
+                const int slot = slot_of[(size_t)token * top + j];
+                if (slot < 0) continue;
+                const float w = weights[(size_t)token * top + j];
+                const float4 v = load4(y + (size_t)slot * hidden + 4 * (size_t)i);
+                kept[n].x = fmaf(w, v.x, kept[n].x), kept[n].y = fmaf(w, v.y, kept[n].y);
+                kept[n].z = fmaf(w, v.z, kept[n].z), kept[n].w = fmaf(w, v.w, kept[n].w);
+            }
+            acc += (kept[n].x * kept[n].x + kept[n].y * kept[n].y) + (kept[n].z * kept[n].z + kept[n].w * kept[n].w);
+        }
+    }
+    const float variance = block_sum(acc, scratch) / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    float4* dst = reinterpret_cast<float4*>(resid + (size_t)token * hidden);
+    const float4* w4 = reinterpret_cast<const float4*>(norm_weight);
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < quads) {
+            float4 r = dst[i];
+            const float4 w = w4[i];
+            r.x += kept[n].x * scale * w.x, r.y += kept[n].y * scale * w.y, r.z += kept[n].z * scale * w.z, r.w += kept[n].w * scale * w.w;
+            dst[i] = r;
+            if (copy) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(copy + (size_t)token * hidden + 4 * (size_t)i) = packed;
+            }
+        }
+    }
+}
+
+// Refuses (KIRAI_ERR_UNSUPPORTED) widths that are no multiple of 4 or above 8,192 and buffers off 16-byte boundaries: the
+// caller then runs route_combine and the norm kernel one after the other.
+KIRAI_EXPORT int kirai_route_combine_norm_add_bf16(float* resid, const void* y, const int* slot_of, const float* weights,
+                                                   const float* norm_weight, void* copy, int tokens, int hidden, int top, float eps,
+                                                   cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (hidden <= 0 || top <= 0) return KIRAI_ERR_BAD_SIZE;
+    if (hidden % 4 != 0 || hidden > 4 * 4 * 512 ||
+        (((uintptr_t)resid | (uintptr_t)y | (uintptr_t)norm_weight | (uintptr_t)copy) & 15) != 0)
+        return KIRAI_ERR_UNSUPPORTED;
+    const int threads = hidden <= 4 * 4 * 128 ? 128 : (hidden <= 4 * 4 * 256 ? 256 : 512);
+    return launch_pdl(route_combine_norm_add_kernel<4>, dim3(tokens), dim3(threads), 0, stream, 1u, resid, (const bf16*)y, slot_of,
+                      weights, norm_weight, (bf16*)copy, hidden, top, eps);
+}

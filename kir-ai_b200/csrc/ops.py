@@ -447,6 +447,28 @@ def route_combine(y: torch.Tensor, slot_of: torch.Tensor, weights: torch.Tensor)
     return out
 
 
+def route_combine_norm_add_takes(hidden: int) -> bool:
+    """Whether ``route_combine_norm_add`` takes rows of this width (a multiple of 4 up to 8,192)."""
+    return hidden % 4 == 0 and 0 < hidden <= 8192
+
+
+def route_combine_norm_add(resid: torch.Tensor, y: torch.Tensor, slot_of: torch.Tensor, weights: torch.Tensor,
+                           norm_weight: torch.Tensor, eps: float, copy_dtype: Optional[torch.dtype] = None):
+    """``route_combine`` and ``norm_add`` in one pass: ``resid`` (32-bit, in place) += RMSNorm(sum_j weights[t, j] *
+    y[slot_of[t, j]]) with ``norm_weight``; the weighted sum is formed in 32-bit and never written out.  ``y`` [slots, H]
+    bfloat16.  Returns the stream's bfloat16 copy when ``copy_dtype`` asks for it."""
+    _need_cuda(resid, y, slot_of, weights, norm_weight)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    assert y.dtype == torch.bfloat16 and y.dim() == 2 and y.is_contiguous() and y.shape[1] == resid.shape[1]
+    assert slot_of.dtype == torch.int32 and slot_of.is_contiguous() and slot_of.shape[0] == resid.shape[0]
+    assert weights.dtype == torch.float32 and weights.shape == slot_of.shape and weights.is_contiguous()
+    assert norm_weight.dtype == torch.float32 and norm_weight.numel() == resid.shape[1] and norm_weight.is_contiguous()
+    copy = torch.empty(resid.shape, dtype=torch.bfloat16, device=resid.device) if copy_dtype == torch.bfloat16 else None
+    _call("kirai_route_combine_norm_add_bf16", _ptr(resid), _ptr(y), _ptr(slot_of), _ptr(weights), _ptr(norm_weight), _ptr(copy),
+          _i(resid.shape[0]), _i(resid.shape[1]), _i(slot_of.shape[1]), _f(eps), _stream())
+    return copy
+
+
 def linear_grouped(x: torch.Tensor, weight, groups: int, tile_group: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                    relu2: bool = False) -> torch.Tensor:
     """Rows sorted by group times one of ``groups`` stacked matrices each: ``x`` [tiles * 128, K] (bfloat16), ``weight``

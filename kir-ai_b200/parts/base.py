@@ -202,7 +202,9 @@ class FeedForward(Part):
     """Token-wise transformation: ``forward(x, batch)`` maps [T, H] to [T, H].
 
     Optional, as for a mixer: ``takes_unscaled(rows)`` and ``fuses_into_norm(rows)`` with
-    ``forward_into_norm(x, batch, resid, spec)``."""
+    ``forward_into_norm(x, batch, resid, spec)``; and, for a block that norms the part's output, ``adds_normed(rows)``
+    with ``forward_add_normed(x, batch, resid, spec)``, which adds the normed output into the 32-bit stream and returns
+    the stream's runtime-dtype copy."""
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
         raise NotImplementedError

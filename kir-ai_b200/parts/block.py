@@ -115,7 +115,7 @@ class Block(Part):
         return resid, m
 
     def _forward_out_norm(self, resid, delta, batch, cache, write_cache):
-        ops, narrow = self.rt.ops, self.rt.dtype != torch.float32
+        ops, narrow, rows = self.rt.ops, self.rt.dtype != torch.float32, resid.shape[0]
         if isinstance(delta, UnscaledNorm):
             raise ValueError("an out_norm block cannot follow a block that folded this block's norm into its product")
         if isinstance(delta, StreamCopy):
@@ -128,5 +128,11 @@ class Block(Part):
             x = ops.round_rows(resid) if narrow else resid
         x = self.norm1.add_normed(resid, self.mixer.forward(x, batch, cache, write_cache))
         if self.ffn is not None:
-            x = self.norm2.add_normed(resid, self.ffn.forward(x if narrow else resid, batch))
+            # a feed-forward may take the norm on its output over (``adds_normed``), as products take over the norms
+            # around them in the pre_norm arrangement
+            spec = self._spec(self.norm2) if _offers(self.ffn, "adds_normed", rows) else None
+            if spec is not None:
+                x = self.ffn.forward_add_normed(x, batch, resid, spec)
+            else:
+                x = self.norm2.add_normed(resid, self.ffn.forward(x if narrow else resid, batch))
         return resid, StreamCopy(x if narrow else None)

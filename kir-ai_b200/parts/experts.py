@@ -93,14 +93,32 @@ class RoutedExperts(FeedForward):
             return ops.router_choose_(self.router_product.forward(x, torch.float32), self.top, want_chosen)
         return ops.router_gates(x, self.router, self.top, want_chosen)
 
+    def _sorts(self, rows: int) -> bool:
+        return self.grouped and rows * self.top >= GROUPED_MIN_ROWS
+
+    def _sorted_rows(self, x: torch.Tensor):
+        """The many-token path up to the experts' outputs: (y [slots, E] bfloat16, slot_of, routing weights)."""
+        ops = self.rt.ops
+        _, ids, mix = self._route(x, True)
+        tile_group, slot_of, row_of_slot = ops.route_plan(ids, self.experts)
+        rows = ops.route_gather(x, row_of_slot)
+        hidden = ops.linear_grouped(rows, self.up.weight, self.experts, tile_group, relu2=True)
+        return ops.linear_grouped(hidden, self.down_stacked.weight, self.experts, tile_group), slot_of, mix
+
+    def adds_normed(self, rows: int) -> bool:
+        """Optional, for a block that norms this part's OUTPUT: whether, for a batch of ``rows`` tokens, the part has
+        ``forward_add_normed(x, batch, resid, spec)``, which adds the normed output into the 32-bit stream itself (the
+        weighted sum of a token's expert rows is then never written out) and returns the stream's runtime-dtype copy."""
+        return self._sorts(rows) and self.rt.ops.route_combine_norm_add_takes(self.hidden_size)
+
+    def forward_add_normed(self, x: torch.Tensor, batch, resid: torch.Tensor, spec):
+        y, slot_of, mix = self._sorted_rows(x)
+        return self.rt.ops.route_combine_norm_add(resid, y, slot_of, mix, spec.weight, spec.eps, self.rt.dtype)
+
     def forward(self, x: torch.Tensor, batch=None) -> torch.Tensor:
         ops = self.rt.ops
-        if self.grouped and x.shape[0] * self.top >= GROUPED_MIN_ROWS:
-            _, ids, mix = self._route(x, True)
-            tile_group, slot_of, row_of_slot = ops.route_plan(ids, self.experts)
-            rows = ops.route_gather(x, row_of_slot)
-            hidden = ops.linear_grouped(rows, self.up.weight, self.experts, tile_group, relu2=True)
-            y = ops.linear_grouped(hidden, self.down_stacked.weight, self.experts, tile_group)
+        if self._sorts(x.shape[0]):
+            y, slot_of, mix = self._sorted_rows(x)
             out = ops.route_combine(y, slot_of, mix)
             return out if self.out_dtype == torch.float32 else ops.round_rows(out)
         gates = self._route(x, False)

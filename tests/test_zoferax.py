@@ -224,7 +224,21 @@ def test_routed_experts_sorted_by_expert(count, top, ff, width, tokens):
     assert float((got - expected).abs().max()) <= tolerance(torch.bfloat16, expected)
     few = torch.cat([part.forward(x[i : i + 100].to(DEV)).cpu() for i in range(0, tokens, 100)])
     assert float((got - few).abs().max()) <= tolerance(torch.bfloat16, expected)
+    # the norm on the output taken over by the part: the same stream as the part's output through the norm kernel
+    from kirai_b200.parts import RMSNorm
+
+    norm = RMSNorm("n", width, 1e-4)
+    load_part(norm, torch.bfloat16, seed=3)
+    stream = torch.randn(tokens, width, generator=torch.Generator().manual_seed(4))
+    apart, fused = stream.clone().to(DEV), stream.clone().to(DEV)
+    copy_apart = norm.add_normed(apart, part.forward(x.to(DEV)))
+    assert part.adds_normed(tokens) and not part.adds_normed(GROUPED_FEW)
+    copy_fused = part.forward_add_normed(x.to(DEV), None, fused, norm.fused_spec())
+    assert float((apart - fused).abs().max()) < 1e-5 and float((copy_apart.float() - copy_fused.float()).abs().max()) < 0.02
     part.rt.ops.check_device_errors(DEV)
+
+
+GROUPED_FEW = 8  # a step of this many tokens takes the few-token path
 
 
 def _attention_part(mixer, width, shares=False):
@@ -581,6 +595,22 @@ def test_greedy_generation_through_the_engine(tiny, dtype):
     assert compared >= 3
     stats = engine.stats()
     assert stats["cache"]["live_requests"] == 0 and all(g["used"] == 0 for g in stats["cache"]["groups"])
+
+
+@pytest.mark.gpu
+def test_eviction_and_recompute_give_the_same_sampled_tokens(tiny):
+    """Seeded temperature sampling on a pool too small for both requests: one is evicted, its pages (of every layer
+    that has keys of its own) go back, and its recomputation gives the tokens of the roomy run."""
+    from kirai_b200 import Engine, SamplingParams
+
+    params = SamplingParams(temperature=0.8, top_p=0.95, seed=5, max_new_tokens=14)
+    prompts = [random_tokens(17, tiny["raw"]["vocab"], 1), random_tokens(18, tiny["raw"]["vocab"], 2)]
+    roomy = Engine(tiny["folder"], dtype="float32", page_size=tiny["page"], max_new_tokens=16, max_cache_tokens=256)
+    expected = [o.token_ids for o in roomy.generate(prompts, params)]
+    tight = Engine(tiny["folder"], dtype="float32", page_size=tiny["page"], max_new_tokens=16, max_cache_tokens=48)
+    outputs = tight.generate(prompts, params)
+    assert [o.token_ids for o in outputs] == expected
+    assert tight.stats()["scheduler"]["preemptions"] >= 1 and sum(o.preemptions for o in outputs) >= 1
 
 
 @pytest.mark.gpu
