@@ -254,7 +254,9 @@ def _attention_part(mixer, width, shares=False):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mixer,width,page", [(attention(4, 2, 16, 8, 0.8), 64, 4), (attention(6, 1, 12, 20, 0.9), 100, 8),
                                               (attention(3, 3, 20, 4, 0.6), 40, 16), (attention(2, 1, 64, 64, 0.2), 32, 2),
-                                              (attention(2, 1, 10, 6, 1.0), 30, 16), (attention(40, 2, 8, 8, 1.0), 64, 32)])
+                                              (attention(2, 1, 10, 6, 1.0), 30, 16), (attention(40, 2, 8, 8, 1.0), 64, 32),
+                                              (attention(4, 2, 96, 48, 0.1), 64, 16), (attention(3, 1, 48, 80, 0.2), 48, 16),
+                                              (attention(2, 2, 128, 64, 0.08), 64, 64), (attention(2, 1, 136, 8, 0.08), 32, 16)])
 def test_attention_part_whole_in_portions_and_one_by_one(dtype, mixer, width, page):
     """One attention layer over 150 tokens: whole, in uneven portions, and token by token, against the plain function;
     then a second request on pages that the first gave back."""
@@ -527,17 +529,29 @@ CONFIG_R = {
 }
 
 
+# S: sizes between the tiny ones and a real model's: heads of 96 with values of 48 (cache rows that are no power of two),
+# eight experts, three layers of which the middle one shares and has no feed-forward.
+CONFIG_S = {
+    "architecture": "Zoferax", "width": 256, "vocab": 160, "embedding": {"scale": 16.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        layer(attention(4, 2, 96, 48, 0.1), experts(8, 2, 64)),
+        layer(attention(8, 2, 96, 48, 0.1, kv_from=0), None),
+        layer(attention(2, 1, 40, 72, 0.15), experts(8, 2, 64)),
+    ],
+}
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_steps_of_many_tokens_sort_rows_by_expert(dtype, tmp_path):
-    """A prompt of 400 tokens in one step (800 and 400 pairs of token and expert: the first layer sorts them, in
+@pytest.mark.parametrize("raw", [CONFIG_R, CONFIG_S], ids=["R", "S"])
+def test_long_prompts_whole_in_portions_and_beside_decoded_tokens(raw, dtype, tmp_path):
+    """A prompt of 400 tokens in one step (in R 800 and 400 pairs of token and expert: the first layer sorts them, in
     bfloat16), then in portions that stay below the threshold, then a mixed step in which a long portion rides beside
     decoded tokens of another request: the same logits every way."""
     from replay_client import Replay
-    from kirai_b200.csrc import ops
 
     folder = str(tmp_path / "model")
-    write_model(folder, CONFIG_R, 6)
+    write_model(folder, raw, 6)
     config, weights = read_model_folder(folder)
     long_tokens, short_tokens = random_tokens(400, 160, 31), random_tokens(40, 160, 32)
     reference = {"long": reference_with_close_calls(config, weights, long_tokens),
