@@ -437,7 +437,7 @@ def main() -> int:
     parser.add_argument("--no-check", action="store_true",
                         help="skip the check of the captured decode step against the step function before each timing")
     parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b", "decode-stamps", "designs"],
-                        help="decode: the contract's measurement (default).  serving-4b: 64 requests with prompts of "
+                        help="decode: the default measurement, whose one JSON line the driver reads.  serving-4b: 64 requests with prompts of "
                              "128..4096 tokens, 512-token prefill portions mixed with decode, 256 new tokens each, greedy, "
                              "Qwen3-4B shape.  batch-32b: 16 requests of 8,064 prompt tokens, 128 new tokens at temperature 1, "
                              "Qwen3-32B shape.  Both run through Engine.generate and print their own one line.  decode-stamps: "
