@@ -73,7 +73,7 @@ struct WarpState {
 template <int D, int BN, int QROWS, bool Q_IN_REGS>
 __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, int q_row0, const uint32_t (*q_regs)[4], uint32_t k_smem,
                                             uint32_t v_smem, int j0, const int (&lo)[2], const int (&hi)[2],
-                                            float scale_log2, int lane) {
+                                            const ScoreForm& form, int lane) {
     float s[BN / 8][4];
 #pragma unroll
     for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
@@ -109,7 +109,7 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
             const int r = e >> 1;
             const int j = col0 + n * 8 + (e & 1);
             const bool visible = j >= lo[r] && j <= hi[r];
-            s[n][e] = visible ? s[n][e] * scale_log2 : -INFINITY;
+            s[n][e] = visible ? score_exponent(s[n][e], form) : -INFINITY;
             m_new[r] = fmaxf(m_new[r], s[n][e]);
         }
     }
@@ -252,7 +252,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
                          const int* __restrict__ block_table, const int* __restrict__ query_start,
                          const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim,
                          long q_row_stride, int page_size, int box_rows, int table_width, int num_pages, int window,
-                         float scale_log2, int* __restrict__ error_flag) {
+                         ScoreForm form, int* __restrict__ error_flag) {
     pdl_launch_dependents();
     pdl_wait();
     using Smem = PrefillSmem<D>;
@@ -311,7 +311,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
     const int last_row = min(rows_total, row0 + PF_ROWS) - 1;
     const int pos_first = start_pos + row0 / group;
     const int pos_last = start_pos + last_row / group;
-    const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int key_lo = first_visible_key(pos_first, window);
     const int first_tile = key_lo / PF_BN, last_tile = pos_last / PF_BN;
     const int num_tiles = last_tile - first_tile + 1;
     bool ok = true;
@@ -354,7 +354,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
         if (row < rows_total) {
             const int pos = start_pos + row / group;
             hi[r] = pos;
-            lo[r] = window > 0 ? max(0, pos - window + 1) : 0;
+            lo[r] = first_visible_key(pos, window);
         } else {
             hi[r] = -1;
             lo[r] = 0;  // sees nothing
@@ -375,7 +375,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
     const int warp_first_row = row0 + warp * 16;
     const int warp_last_row = min(rows_total - 1, warp_first_row + 15);
     const int warp_pos_last = warp_first_row < rows_total ? start_pos + warp_last_row / group : -1;
-    const int warp_key_lo = (window > 0 && warp_first_row < rows_total) ? max(0, start_pos + warp_first_row / group - window + 1) : 0;
+    const int warp_key_lo = warp_first_row < rows_total ? first_visible_key(start_pos + warp_first_row / group, window) : 0;
     for (int it = 0; it < num_tiles; ++it) {
         const int slot = it % PF_STAGES;
         const int t = first_tile + it;
@@ -388,7 +388,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
         if (warp_active) {
             const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
             warp_attend<D, PF_BN, PF_ROWS, Q_IN_REGS>(st, q_smem, warp * 16, q_regs, k_s, k_s + Smem::tile_bytes, t * PF_BN, lo, hi,
-                                                     scale_log2, lane);
+                                                     form, lane);
         }
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive(sm100::smem_addr(&empty_bar[slot]));
@@ -439,7 +439,7 @@ struct HeadState {
 // q_b[kk] are the B-operand fragments of Q^T for dims 16 kk .. 16 kk + 15.
 template <int D, int BN>
 __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32_t (*q_b)[2], uint32_t k_smem,
-                                                  uint32_t v_smem, int j0, int lo, int hi, float scale_log2, int lane) {
+                                                  uint32_t v_smem, int j0, int lo, int hi, const ScoreForm& form, int lane) {
     constexpr int MT = BN / 16;
     float s[MT][4];
 #pragma unroll
@@ -462,7 +462,7 @@ __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32
         for (int e = 0; e < 4; ++e) {
             const int j = j0 + mt * 16 + g + (e >> 1) * 8;
             const bool visible = interior || (j >= lo && j <= hi);
-            s[mt][e] = visible ? s[mt][e] * scale_log2 : -INFINITY;
+            s[mt][e] = visible ? score_exponent(s[mt][e], form) : -INFINITY;
             m_new[e & 1] = fmaxf(m_new[e & 1], s[mt][e]);
         }
     }
@@ -559,7 +559,7 @@ struct DecodeArgs {
     int q_heads, kv_heads, head_dim;
     long q_row_stride;
     int page_size, box_rows, table_width, num_pages, window;
-    float scale_log2;
+    ScoreForm form;
     int* error_flag;
     // Fused preparation (fuse != 0; head_dim is then the template's D): q points to the rows that the q, k, v product
     // left, [requests, (q_heads + 2 kv_heads) * head_dim] with row stride q_row_stride, untouched.  Every CTA norms and
@@ -706,7 +706,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
     constexpr int PANELS = D / 64;
     const int q_heads = args.q_heads, kv_heads = args.kv_heads, head_dim = args.head_dim;
     const int page_size = args.page_size, table_width = args.table_width;
-    const float scale_log2 = args.scale_log2;
+    const ScoreForm form = args.form;
     const int group = q_heads / kv_heads;  // <= 16 rows
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t q_smem = sm100::smem_addr(smem);
@@ -847,7 +847,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
             const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
             if (args.fuse && my_first + k * DC_WARPS == last_tile)
                 append_new_token<D, BN>(args, rope_s, k_weight_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
-            warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, key_lo, pos, scale_log2, lane);
+            warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, key_lo, pos, form, lane);
             __syncwarp();
             if (k + DC_STAGES < my_count) issue(my_first + (k + DC_STAGES) * DC_WARPS, slot);
         }
@@ -902,7 +902,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         if (args.fuse && my_first + k * DC_WARPS == last_tile)
             append_new_token<D, BN>(args, rope_s, k_weight_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
         warp_attend<D, BN, 16, Q_IN_REGS>(st, q_smem, 0, q_regs, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, lo, hi,
-                                          scale_log2, lane);
+                                          form, lane);
         __syncwarp();
         if (k + DC_STAGES < my_count) issue(my_first + (k + DC_STAGES) * DC_WARPS, slot);
     }
@@ -998,7 +998,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
     const int split = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
     const int group = args.q_heads / args.kv_heads;
     const int pos = context_len[req] - 1;
-    const int key_lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
+    const int key_lo = first_visible_key(pos, args.window);
     const int first_tile = key_lo / BN, last_tile = pos / BN;
     const int tiles = last_tile - first_tile + 1;
     const int per_split = (tiles + num_splits - 1) / num_splits;
@@ -1059,7 +1059,7 @@ __device__ __forceinline__ void decode_tile_prefix(const int* __restrict__ conte
         const int pos = context_len[r] - 1;
         int tiles = 0;
         if (pos >= 0) {
-            const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+            const int key_lo = first_visible_key(pos, window);
             tiles = pos / tile_keys - key_lo / tile_keys + 1;
         }
         prefix[r + 1] = tiles;
@@ -1123,7 +1123,7 @@ attention_decode_balanced_kernel(const __grid_constant__ CUtensorMap kv_map, Dec
         const int tiles = prefix[req + 1] - prefix[req];
         if (tiles == 0) continue;
         const int pos = context_len[req] - 1;
-        const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int key_lo = first_visible_key(pos, window);
         const int first_tile = key_lo / BN, last_tile = pos / BN;
         const int head_first = begin > pair_begin ? (int)((begin - pair_begin) / tiles) : 0;
         for (int kv_head = head_first; kv_head < kv_heads; ++kv_head) {
@@ -1246,7 +1246,7 @@ template <int D>
 int prefill_launch(const void* q, const void* cache, void* out, const int* block_table, const int* query_start,
                    const int* context_len, int requests, int max_query_len, int q_heads, int kv_heads, int head_dim,
                    long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale,
-                   int* error_flag, cudaStream_t stream) {
+                   int* error_flag, cudaStream_t stream, float softcap = 0.0f) {
     using Smem = PrefillSmem<D>;
     const int group = q_heads / kv_heads;
     const int box_rows = page_size < PF_BN ? page_size : PF_BN;
@@ -1261,14 +1261,14 @@ int prefill_launch(const void* q, const void* cache, void* out, const int* block
     if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
     return launch_pdl(kernel, grid, dim3((PF_WARPS + 1) * 32), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q,
                       (bf16*)out, block_table, query_start, context_len, q_heads, kv_heads, head_dim, q_row_stride,
-                      page_size, box_rows, table_width, num_pages, window, scale * 1.4426950408889634f, error_flag);
+                      page_size, box_rows, table_width, num_pages, window, make_score_form(scale, softcap), error_flag);
 }
 
 template <int D>
 int decode_launch(const void* q, const void* cache, void* out, float* partial, const int* block_table,
                   const int* context_len, int requests, int q_heads, int kv_heads, int head_dim, long q_row_stride,
                   int page_size, int table_width, int num_pages, int window, float scale, int num_splits,
-                  int* error_flag, cudaStream_t stream, const FuseQK* fuse = nullptr) {
+                  int* error_flag, cudaStream_t stream, const FuseQK* fuse = nullptr, float softcap = 0.0f) {
     using Smem = DecodeSmem<D>;
     const int box_rows = page_size < Smem::BN ? page_size : Smem::BN;
     if (Smem::BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;  // page sizes: powers of two
@@ -1285,7 +1285,7 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     if (err != cudaSuccess) return (int)err;
     if (fuse && head_dim != D) return KIRAI_ERR_UNSUPPORTED;  // the fused preparation works on whole heads of 64, 128 or 256
     DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
-                    table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
+                    table_width, num_pages, window, make_score_form(scale, softcap), error_flag};
     if (fuse) {
         args.fuse = 1, args.q_weight = fuse->q_weight, args.k_weight = fuse->k_weight, args.inv_freq = fuse->inv_freq;
         args.eps = fuse->eps, args.cache = (bf16*)const_cast<void*>(cache);
@@ -1307,7 +1307,7 @@ template <int D>
 int decode_balanced_launch(const void* q, const void* cache, void* out, float* partial, const int* block_table,
                            const int* context_len, int requests, int q_heads, int kv_heads, int head_dim,
                            long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale,
-                           int ctas, int* error_flag, cudaStream_t stream, const FuseQK* fuse = nullptr) {
+                           int ctas, int* error_flag, cudaStream_t stream, const FuseQK* fuse = nullptr, float softcap = 0.0f) {
     using Smem = DecodeSmem<D>;
     const int box_rows = page_size < Smem::BN ? page_size : Smem::BN;
     if (Smem::BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;  // page sizes: powers of two
@@ -1319,7 +1319,7 @@ int decode_balanced_launch(const void* q, const void* cache, void* out, float* p
     if (err != cudaSuccess) return (int)err;
     if (fuse && head_dim != D) return KIRAI_ERR_UNSUPPORTED;  // the fused preparation works on whole heads of 64, 128 or 256
     DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
-                    table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
+                    table_width, num_pages, window, make_score_form(scale, softcap), error_flag};
     if (fuse) {
         args.fuse = 1, args.q_weight = fuse->q_weight, args.k_weight = fuse->k_weight, args.inv_freq = fuse->inv_freq;
         args.eps = fuse->eps, args.cache = (bf16*)const_cast<void*>(cache);
@@ -1345,11 +1345,11 @@ int check_common(int q_heads, int kv_heads, int head_dim, long q_row_stride, con
 // Attention for the new tokens of a step: q [tokens, q_heads, head_dim] (row stride in elements),
 // requests described by query_start [requests + 1] and context_len [requests] (tokens in the cache
 // after this step, the new ones included).  out [tokens, q_heads * head_dim].
-KIRAI_EXPORT int kirai_attention_prefill_bf16(const void* q, const void* cache, void* out, const int* block_table,
-                                              const int* query_start, const int* context_len, int requests,
-                                              int max_query_len, int q_heads, int kv_heads, int head_dim,
-                                              long q_row_stride, int page_size, int table_width, int num_pages,
-                                              int window, float scale, int* error_flag, cudaStream_t stream) {
+static int attention_prefill_entry(const void* q, const void* cache, void* out, const int* block_table,
+                                   const int* query_start, const int* context_len, int requests,
+                                   int max_query_len, int q_heads, int kv_heads, int head_dim,
+                                   long q_row_stride, int page_size, int table_width, int num_pages,
+                                   int window, float scale, float softcap, int* error_flag, cudaStream_t stream) {
     if (requests <= 0 || max_query_len <= 0) return 0;
     int bad = check_common(q_heads, kv_heads, head_dim, q_row_stride, q);
     if (bad) return bad;
@@ -1357,11 +1357,34 @@ KIRAI_EXPORT int kirai_attention_prefill_bf16(const void* q, const void* cache, 
 #define KIRAI_PF(D) \
     return prefill_launch<D>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, \
                              kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, \
-                             error_flag, stream)
+                             error_flag, stream, softcap)
     if (head_dim <= 64) KIRAI_PF(64);
     if (head_dim <= 128) KIRAI_PF(128);
     KIRAI_PF(256);
 #undef KIRAI_PF
+}
+
+KIRAI_EXPORT int kirai_attention_prefill_bf16(const void* q, const void* cache, void* out, const int* block_table,
+                                              const int* query_start, const int* context_len, int requests,
+                                              int max_query_len, int q_heads, int kv_heads, int head_dim,
+                                              long q_row_stride, int page_size, int table_width, int num_pages,
+                                              int window, float scale, int* error_flag, cudaStream_t stream) {
+    return attention_prefill_entry(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads,
+                                   kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, 0.0f,
+                                   error_flag, stream);
+}
+
+// The same with a soft cap on the scores: score <- softcap * tanh(score / softcap) before the softmax (0: none), and
+// with `window` < 0 for a chunked mask (see first_visible_key).
+KIRAI_EXPORT int kirai_attention_prefill_softcap_bf16(const void* q, const void* cache, void* out, const int* block_table,
+                                                      const int* query_start, const int* context_len, int requests,
+                                                      int max_query_len, int q_heads, int kv_heads, int head_dim,
+                                                      long q_row_stride, int page_size, int table_width, int num_pages,
+                                                      int window, float scale, float softcap, int* error_flag,
+                                                      cudaStream_t stream) {
+    return attention_prefill_entry(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads,
+                                   kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages, window, scale,
+                                   softcap, error_flag, stream);
 }
 
 // How many clusters of `cluster` CTAs of the decode kernel the device can hold at once, 0 if it refuses the size.
@@ -1400,11 +1423,11 @@ KIRAI_EXPORT int kirai_attention_decode_resident_clusters(int head_dim, int grou
 // Attention for a batch in which every request brings exactly one token (token r belongs to request r).
 // With num_splits > 1 and a buffer `partial` of requests * q_heads * num_splits * (head_dim + 2) floats, the ranges'
 // results go through that buffer and a second kernel merges them.
-KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, void* out, float* partial,
-                                             const int* block_table, const int* context_len, int requests,
-                                             int q_heads, int kv_heads, int head_dim, long q_row_stride, int page_size,
-                                             int table_width, int num_pages, int window, float scale, int num_splits,
-                                             int* error_flag, cudaStream_t stream) {
+static int attention_decode_entry(const void* q, const void* cache, void* out, float* partial,
+                                  const int* block_table, const int* context_len, int requests,
+                                  int q_heads, int kv_heads, int head_dim, long q_row_stride, int page_size,
+                                  int table_width, int num_pages, int window, float scale, float softcap, int num_splits,
+                                  int* error_flag, cudaStream_t stream) {
     if (requests <= 0) return 0;
     int bad = check_common(q_heads, kv_heads, head_dim, q_row_stride, q);
     if (bad) return bad;
@@ -1414,20 +1437,41 @@ KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, v
 #define KIRAI_DC(D) \
     return decode_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim, \
                             q_row_stride, page_size, table_width, num_pages, window, scale, num_splits, error_flag, \
-                            stream)
+                            stream, nullptr, softcap)
     if (head_dim <= 64) KIRAI_DC(64);
     if (head_dim <= 128) KIRAI_DC(128);
     KIRAI_DC(256);
 #undef KIRAI_DC
 }
 
+KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, void* out, float* partial,
+                                             const int* block_table, const int* context_len, int requests,
+                                             int q_heads, int kv_heads, int head_dim, long q_row_stride, int page_size,
+                                             int table_width, int num_pages, int window, float scale, int num_splits,
+                                             int* error_flag, cudaStream_t stream) {
+    return attention_decode_entry(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim,
+                                  q_row_stride, page_size, table_width, num_pages, window, scale, 0.0f, num_splits, error_flag,
+                                  stream);
+}
+
+// The same with a soft cap on the scores (0: none) and `window` < 0 for a chunked mask.
+KIRAI_EXPORT int kirai_attention_decode_softcap_bf16(const void* q, const void* cache, void* out, float* partial,
+                                                     const int* block_table, const int* context_len, int requests,
+                                                     int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                                                     int page_size, int table_width, int num_pages, int window, float scale,
+                                                     float softcap, int num_splits, int* error_flag, cudaStream_t stream) {
+    return attention_decode_entry(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim,
+                                  q_row_stride, page_size, table_width, num_pages, window, scale, softcap, num_splits,
+                                  error_flag, stream);
+}
+
 // The same with the work cut evenly: `ctas` CTAs (one per SM is the intent) each attend the same number of key
 // tiles, whatever the batch size and the context lengths are.  partial holds ctas * 2 * 16 * (head_dim + 2) floats.
-KIRAI_EXPORT int kirai_attention_decode_balanced_bf16(const void* q, const void* cache, void* out, float* partial,
-                                                      const int* block_table, const int* context_len, int requests,
-                                                      int q_heads, int kv_heads, int head_dim, long q_row_stride,
-                                                      int page_size, int table_width, int num_pages, int window,
-                                                      float scale, int ctas, int* error_flag, cudaStream_t stream) {
+static int attention_decode_balanced_entry(const void* q, const void* cache, void* out, float* partial,
+                                           const int* block_table, const int* context_len, int requests,
+                                           int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                                           int page_size, int table_width, int num_pages, int window,
+                                           float scale, float softcap, int ctas, int* error_flag, cudaStream_t stream) {
     if (requests <= 0) return 0;
     int bad = check_common(q_heads, kv_heads, head_dim, q_row_stride, q);
     if (bad) return bad;
@@ -1437,11 +1481,33 @@ KIRAI_EXPORT int kirai_attention_decode_balanced_bf16(const void* q, const void*
 #define KIRAI_DCB(D) \
     return decode_balanced_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, \
                                      head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, ctas, \
-                                     error_flag, stream)
+                                     error_flag, stream, nullptr, softcap)
     if (head_dim <= 64) KIRAI_DCB(64);
     if (head_dim <= 128) KIRAI_DCB(128);
     KIRAI_DCB(256);
 #undef KIRAI_DCB
+}
+
+KIRAI_EXPORT int kirai_attention_decode_balanced_bf16(const void* q, const void* cache, void* out, float* partial,
+                                                      const int* block_table, const int* context_len, int requests,
+                                                      int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                                                      int page_size, int table_width, int num_pages, int window,
+                                                      float scale, int ctas, int* error_flag, cudaStream_t stream) {
+    return attention_decode_balanced_entry(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads,
+                                           head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, 0.0f, ctas,
+                                           error_flag, stream);
+}
+
+// The same with a soft cap on the scores (0: none) and `window` < 0 for a chunked mask.
+KIRAI_EXPORT int kirai_attention_decode_balanced_softcap_bf16(const void* q, const void* cache, void* out, float* partial,
+                                                              const int* block_table, const int* context_len, int requests,
+                                                              int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                                                              int page_size, int table_width, int num_pages, int window,
+                                                              float scale, float softcap, int ctas, int* error_flag,
+                                                              cudaStream_t stream) {
+    return attention_decode_balanced_entry(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads,
+                                           head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, softcap,
+                                           ctas, error_flag, stream);
 }
 
 // The two decode entry points with the preparation of queries and keys inside: `qkv` holds the rows that the q, k, v

@@ -21,7 +21,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ cach
                              const int* __restrict__ block_table, const int* __restrict__ request_of_token,
                              const int* __restrict__ positions, int q_heads, int kv_heads, int head_dim,
                              long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale,
-                             int* __restrict__ error_flag) {
+                             float softcap, int* __restrict__ error_flag) {
     extern __shared__ float smem[];
     float* q_s = smem;                       // [head_dim]
     float* o_s = smem + head_dim;            // [ATT_WARPS][head_dim]
@@ -33,7 +33,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ cach
     const int kv_head = head / (q_heads / kv_heads);
     const int pos = positions[token];
     const int* table = block_table + (long)request_of_token[token] * table_width;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = first_visible_key(pos, window);
 
     const T* q_row = q + (size_t)token * q_row_stride + (size_t)head * head_dim;
     for (int i = threadIdx.x; i < head_dim; i += blockDim.x) q_s[i] = to_f32<T>(q_row[i]);
@@ -57,6 +57,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ cach
         float dot = 0.0f;
         for (int i = lane; i < head_dim; i += 32) dot = fmaf(q_s[i], to_f32<T>(k_row[i]), dot);
         dot = warp_sum(dot) * scale;
+        if (softcap > 0.0f) dot = softcap * tanhf(dot / softcap);
         const float m_new = fmaxf(m, dot);
         const float corr = expf(m - m_new);  // 0 on the first key (m = -inf)
         const float p = expf(dot - m_new);
@@ -101,7 +102,7 @@ template <typename T>
 static int paged_attention_plain_launch(const void* q, const void* cache, void* out, const int* block_table,
                                         const int* request_of_token, const int* positions, int tokens, int q_heads,
                                         int kv_heads, int head_dim, long q_row_stride, int page_size, int table_width,
-                                        int num_pages, int window, float scale, int* error_flag, cudaStream_t stream) {
+                                        int num_pages, int window, float scale, float softcap, int* error_flag, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim > 32 * ATT_MAX_PER_LANE || head_dim <= 0) return KIRAI_ERR_BAD_SIZE;
     if (kv_heads <= 0 || q_heads % kv_heads != 0) return KIRAI_ERR_BAD_SIZE;
@@ -110,7 +111,7 @@ static int paged_attention_plain_launch(const void* q, const void* cache, void* 
     dim3 grid(tokens, q_heads);
     paged_attention_plain_kernel<T><<<grid, ATT_WARPS * 32, smem, stream>>>(
         (const T*)q, (const T*)cache, (T*)out, block_table, request_of_token, positions, q_heads, kv_heads, head_dim,
-        q_row_stride, page_size, table_width, num_pages, window, scale, error_flag);
+        q_row_stride, page_size, table_width, num_pages, window, scale, softcap, error_flag);
     return launch_status();
 }
 
@@ -121,7 +122,7 @@ KIRAI_EXPORT int kirai_paged_attention_plain_f32(const void* q, const void* cach
                                                  float scale, int* error_flag, cudaStream_t stream) {
     return paged_attention_plain_launch<float>(q, cache, out, block_table, request_of_token, positions, tokens, q_heads,
                                                kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages,
-                                               window, scale, error_flag, stream);
+                                               window, scale, 0.0f, error_flag, stream);
 }
 KIRAI_EXPORT int kirai_paged_attention_plain_bf16(const void* q, const void* cache, void* out, const int* block_table,
                                                   const int* request_of_token, const int* positions, int tokens,
@@ -130,5 +131,26 @@ KIRAI_EXPORT int kirai_paged_attention_plain_bf16(const void* q, const void* cac
                                                   float scale, int* error_flag, cudaStream_t stream) {
     return paged_attention_plain_launch<bf16>(q, cache, out, block_table, request_of_token, positions, tokens, q_heads,
                                               kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages,
-                                              window, scale, error_flag, stream);
+                                              window, scale, 0.0f, error_flag, stream);
+}
+
+// The same with a soft cap on the scores: score <- softcap * tanh(score / softcap) before the softmax (0: none), and
+// `window` < 0 for a chunked mask (see first_visible_key).
+KIRAI_EXPORT int kirai_paged_attention_plain_softcap_f32(const void* q, const void* cache, void* out, const int* block_table,
+                                                         const int* request_of_token, const int* positions, int tokens,
+                                                         int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                                                         int page_size, int table_width, int num_pages, int window,
+                                                         float scale, float softcap, int* error_flag, cudaStream_t stream) {
+    return paged_attention_plain_launch<float>(q, cache, out, block_table, request_of_token, positions, tokens, q_heads,
+                                               kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages,
+                                               window, scale, softcap, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_paged_attention_plain_softcap_bf16(const void* q, const void* cache, void* out, const int* block_table,
+                                                          const int* request_of_token, const int* positions, int tokens,
+                                                          int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                                                          int page_size, int table_width, int num_pages, int window,
+                                                          float scale, float softcap, int* error_flag, cudaStream_t stream) {
+    return paged_attention_plain_launch<bf16>(q, cache, out, block_table, request_of_token, positions, tokens, q_heads,
+                                              kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages,
+                                              window, scale, softcap, error_flag, stream);
 }

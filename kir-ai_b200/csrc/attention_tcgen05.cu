@@ -129,11 +129,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                             const int* __restrict__ block_table, const int* __restrict__ query_start,
                             const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim,
                             long q_row_stride, int page_size, int box_rows, int piece_rows, int table_width, int num_pages,
-                            int window, float scale_log2, int* __restrict__ error_flag) {
+                            int window, ScoreForm form, int* __restrict__ error_flag) {
     pdl_launch_dependents();
     pdl_wait();
     using Smem = TcAttnSmem<D>;
     constexpr int PANELS = Smem::panels;
+    const float scale_log2 = form.cap_log2 != 0.0f ? 1.0f : form.scale_log2;  // capped scores are in the exponent's units already
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // CTAs are handed out in the order of their linear index, x fastest: the kv heads are x and the row tiles y, last
@@ -167,7 +168,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     const int last_row = min(rows_total, row0 + TA_ROWS) - 1;
     const int pos_first = start_pos + row0 / group;
     const int pos_last = start_pos + last_row / group;
-    const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int key_lo = first_visible_key(pos_first, window);
     const int first_tile = key_lo / TA_BN, last_tile = pos_last / TA_BN;
     const int num_tiles = last_tile - first_tile + 1;
 
@@ -363,7 +364,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         const int row = row0 + r;
         const bool valid = row < rows_total;
         const int pos = valid ? start_pos + row / group : -1;
-        const int lo = (valid && window > 0) ? max(0, pos - window + 1) : 0;
+        const int lo = valid ? first_visible_key(pos, window) : 0;
         float m_used = -INFINITY;  // the maximum that the accumulator and the sum are scaled by (log2 domain)
         float l = 0.0f;
         for (int it = 0; it < num_tiles; ++it) {
@@ -385,6 +386,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                     s[32 + i] = half1[i];
                 }
             }
+            // with a soft cap the scores become cap * tanh(score * scale / cap) * log2(e) here, before the mask, and
+            // the factor below is one
+            if (form.cap_log2 != 0.0f) {
+#pragma unroll
+                for (int i = 0; i < TA_BN; ++i)
+                    s[i] = __float_as_uint(form.cap_log2 * tanh_from_exp(__uint_as_float(s[i]) * form.cap_in));
+            }
             // a tile whose keys every row of this warp sees needs no mask
             const bool interior = __all_sync(0xffffffffu, j0 >= lo && j0 + TA_BN - 1 <= pos);
             if (!interior) {
@@ -398,7 +406,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < TA_BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(s[i]));
-            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;  // the scale is positive
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;  // the factor is positive
             const float m_new = fmaxf(m_used, m_tile);
             const bool grow = m_new > m_used + 8.0f || (m_used == -INFINITY && m_new != -INFINITY);
             const float factor = grow ? exp2f(m_used - m_new) : 1.0f;  // exp2(-inf) = 0 for a row that saw nothing yet
@@ -493,8 +501,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
 template <int D>
 int launch(const void* q, const void* cache, void* out, const int* block_table, const int* query_start,
            const int* context_len, int requests, int max_query_len, int q_heads, int kv_heads, int head_dim,
-           long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale, int* error_flag,
-           cudaStream_t stream) {
+           long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale, float softcap,
+           int* error_flag, cudaStream_t stream) {
     using Smem = TcAttnSmem<D>;
     const int group = q_heads / kv_heads;
     const int box_rows = page_size < TA_BN ? page_size : TA_BN;
@@ -514,18 +522,18 @@ int launch(const void* q, const void* cache, void* out, const int* block_table, 
     if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
     return launch_pdl(kernel, grid, dim3(TA_THREADS), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q, (bf16*)out,
                       block_table, query_start, context_len, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
-                      piece_rows, table_width, num_pages, window, scale * 1.4426950408889634f, error_flag);
+                      piece_rows, table_width, num_pages, window, make_score_form(scale, softcap), error_flag);
 }
 
 }  // namespace
 
 // Same arguments as kirai_attention_prefill_bf16.  Refuses (KIRAI_ERR_UNSUPPORTED) head sizes above
 // 128, groups that do not divide 128, and page sizes that are no power of two.
-KIRAI_EXPORT int kirai_attention_prefill_tc_bf16(const void* q, const void* cache, void* out, const int* block_table,
-                                                 const int* query_start, const int* context_len, int requests,
-                                                 int max_query_len, int q_heads, int kv_heads, int head_dim,
-                                                 long q_row_stride, int page_size, int table_width, int num_pages,
-                                                 int window, float scale, int* error_flag, cudaStream_t stream) {
+static int attention_prefill_tc_entry(const void* q, const void* cache, void* out, const int* block_table,
+                                      const int* query_start, const int* context_len, int requests,
+                                      int max_query_len, int q_heads, int kv_heads, int head_dim,
+                                      long q_row_stride, int page_size, int table_width, int num_pages,
+                                      int window, float scale, float softcap, int* error_flag, cudaStream_t stream) {
     if (requests <= 0 || max_query_len <= 0) return 0;
     if (kv_heads <= 0 || q_heads % kv_heads != 0) return KIRAI_ERR_BAD_SIZE;
     const int group = q_heads / kv_heads;
@@ -535,7 +543,29 @@ KIRAI_EXPORT int kirai_attention_prefill_tc_bf16(const void* q, const void* cach
     if (requests > 65535 || kv_heads > 65535) return KIRAI_ERR_BAD_SIZE;
     if (head_dim <= 64)
         return launch<64>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, kv_heads,
-                          head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, error_flag, stream);
+                          head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, softcap, error_flag, stream);
     return launch<128>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, kv_heads,
-                       head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, error_flag, stream);
+                       head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, softcap, error_flag, stream);
+}
+
+KIRAI_EXPORT int kirai_attention_prefill_tc_bf16(const void* q, const void* cache, void* out, const int* block_table,
+                                                 const int* query_start, const int* context_len, int requests,
+                                                 int max_query_len, int q_heads, int kv_heads, int head_dim,
+                                                 long q_row_stride, int page_size, int table_width, int num_pages,
+                                                 int window, float scale, int* error_flag, cudaStream_t stream) {
+    return attention_prefill_tc_entry(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads,
+                                      kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, 0.0f,
+                                      error_flag, stream);
+}
+
+// The same with a soft cap on the scores (0: none) and `window` < 0 for a chunked mask.
+KIRAI_EXPORT int kirai_attention_prefill_tc_softcap_bf16(const void* q, const void* cache, void* out, const int* block_table,
+                                                         const int* query_start, const int* context_len, int requests,
+                                                         int max_query_len, int q_heads, int kv_heads, int head_dim,
+                                                         long q_row_stride, int page_size, int table_width, int num_pages,
+                                                         int window, float scale, float softcap, int* error_flag,
+                                                         cudaStream_t stream) {
+    return attention_prefill_tc_entry(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads,
+                                      kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages, window, scale,
+                                      softcap, error_flag, stream);
 }

@@ -24,6 +24,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = [
     "elementwise.cu",
     "layer_forms.cu",
+    "mixer_forms.cu",
     "experts.cu",
     "gemm_simt.cu",
     "attention_plain.cu",

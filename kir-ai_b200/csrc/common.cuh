@@ -79,6 +79,41 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return total;
 }
 
+// ---- which keys a query sees, and what becomes of a score -------------------
+// `window` > 0: the last `window` keys up to the query's own position; `window` < 0: the keys of the query's own
+// chunk of -window positions (chunks counted from position 0 of the sequence); 0: every key up to its own position.
+// The first visible key never decreases with the position.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
+// tanh in 32-bit from one exponential: 1 - 2 / (e^(2x) + 1); the absolute error stays near 1e-7.
+__device__ __forceinline__ float tanh_from_exp(float x) {
+    x = fminf(fmaxf(x, -15.0f), 15.0f);             // tanh is +-1 in 32-bit beyond that
+    const float e = exp2f(x * 2.885390081777927f);  // e^(2x)
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
+// A raw score (q . k) in the base-2 exponent's units: times scale * log2(e), or, with a soft cap c,
+// c * tanh(score * scale / c) * log2(e).  cap_log2 = c * log2(e) (0: no cap), cap_in = scale / c.
+struct ScoreForm {
+    float scale_log2, cap_in, cap_log2;
+};
+
+static inline ScoreForm make_score_form(float scale, float softcap) {
+    ScoreForm form;
+    form.scale_log2 = scale * 1.4426950408889634f;
+    form.cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
+    form.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+    return form;
+}
+
+__device__ __forceinline__ float score_exponent(float raw, const ScoreForm& form) {
+    return form.cap_log2 != 0.0f ? form.cap_log2 * tanh_from_exp(raw * form.cap_in) : raw * form.scale_log2;
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // ---- programmatic dependent launch -----------------------------------------

@@ -1,0 +1,605 @@
+// Row-wise kernels of mixers and norms beside those of elementwise.cu and layer_forms.cu:
+//
+//   * layer norm with a weight and no bias, with the residual add (and a bias of the sub-layer before) fused in:
+//     (x - mean) / sqrt(var + eps) * w, var the mean of the squared deviations, statistics in 32-bit;
+//   * token shift: a row h_t becomes h_t + (h_{t-1} - h_t) * mu, h_{t-1} the previous token's row as it was before
+//     the replacement (a request's state slot keeps its last row between steps, zeros at its start);
+//   * the minGRU recurrence S_t = (1 - z_t) S_{t-1} + z_t c_t, element by element, state in 32-bit in the slot,
+//     as a walk over a request's tokens (steps of few tokens) and as a scan over pieces of SCAN_PIECE tokens
+//     (prompt portions): the pieces' (product of 1 - z, end state from zero) first, then every piece's incoming
+//     state, then the rows;
+//   * the preparation of attention with biases, a rotation of a part of each head and a factor per head: queries
+//     out (heads padded to the cache's row width), keys and values to their pages;
+//   * the preparation of latent attention: RMS norms of the query latent and of the key/value latent, rotation of
+//     the shared key part, the latent row to the pages (as key row [latent, rotated part] and as value row [latent]);
+//   * small element-wise steps: a sigmoid gate on padded heads, a gated activation, a bias on rows.
+//
+// What enters a norm, a rotation or a recurrence is read in 32-bit (the products before these kernels leave 32-bit
+// rows); only what a product reads next is rounded to the runtime dtype.
+#include "common.cuh"
+
+// ------------------------------------------------------------ add + layer norm
+// One block per produced row.  resid[row] += delta[row] + delta_bias (when the stream is updated: no row_index);
+// out[row] = LN(resid[row]) * weight.  With row_index only those rows are produced, the stream stays as it is.
+template <typename T, typename O>
+__global__ void add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ delta_bias,
+                                     const float* __restrict__ weight, O* __restrict__ out, const int* __restrict__ row_index,
+                                     int hidden, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float row_s[];  // [hidden]
+    __shared__ float scratch[32];
+    const int produced = blockIdx.x;
+    const size_t row = row_index ? (size_t)row_index[produced] : (size_t)produced;
+    float* x = resid + row * hidden;
+    const T* d = delta ? delta + row * hidden : nullptr;
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[i];
+        if (d) v += to_f32<T>(d[i]);
+        if (delta_bias) v += delta_bias[i];
+        row_s[i] = v;
+        if (!row_index && (d || delta_bias)) x[i] = v;
+        acc += v;
+    }
+    const float mean = block_sum(acc, scratch) / (float)hidden;
+    float dev = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float c = row_s[i] - mean;
+        dev = fmaf(c, c, dev);
+    }
+    const float variance = block_sum(dev, scratch) / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    O* dst = out + (size_t)produced * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<O>((row_s[i] - mean) * scale * weight[i]);
+}
+
+template <typename T, typename O>
+static int add_layernorm_launch(float* resid, const void* delta, const float* delta_bias, const float* weight, void* out,
+                                const int* row_index, int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || (size_t)hidden * sizeof(float) > 200 * 1024) return KIRAI_ERR_BAD_SIZE;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    auto kernel = add_layernorm_kernel<T, O>;
+    if (smem > 48 * 1024) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    return launch_pdl(kernel, dim3(rows), dim3(threads), smem, stream, 1u, resid, (const T*)delta, delta_bias, weight, (O*)out,
+                      row_index, hidden, eps);
+}
+
+// delta in the runtime dtype (f32 / bf16); the normed rows in that dtype, or (``wide``) in 32-bit for a token shift.
+KIRAI_EXPORT int kirai_add_layernorm_f32(float* resid, const void* delta, const float* delta_bias, const float* weight,
+                                         void* out, const int* row_index, int rows, int hidden, float eps, int wide,
+                                         cudaStream_t stream) {
+    return add_layernorm_launch<float, float>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, stream);
+}
+KIRAI_EXPORT int kirai_add_layernorm_bf16(float* resid, const void* delta, const float* delta_bias, const float* weight,
+                                          void* out, const int* row_index, int rows, int hidden, float eps, int wide,
+                                          cudaStream_t stream) {
+    if (wide) return add_layernorm_launch<bf16, float>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, stream);
+    return add_layernorm_launch<bf16, bf16>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, stream);
+}
+
+// ------------------------------------------------------------------ token shift
+// One block per token row.  The row before a request's first row of this step is its slot of `state`; the block of
+// that first row reads the slot and then puts the request's last row of this step there, so no slot is read and
+// written by different blocks.
+template <typename O>
+__global__ void token_shift_kernel(const float* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state,
+                                   const int* __restrict__ request_of_token, const int* __restrict__ query_start,
+                                   const int* __restrict__ slots, O* __restrict__ out, int hidden, int num_slots) {
+    pdl_launch_dependents();
+    const int row = blockIdx.x;
+    const int request = request_of_token[row];
+    const int first = query_start[request], last = query_start[request + 1] - 1;
+    const int slot = slots[request];
+    pdl_wait();
+    const float* cur = h + (size_t)row * hidden;
+    O* dst = out + (size_t)row * hidden;
+    if (row != first) {
+        const float* prev = cur - hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float c = cur[i];
+            dst[i] = from_f32<O>(c + (prev[i] - c) * mu[i]);
+        }
+        return;
+    }
+    if (slot < 0 || slot >= num_slots) return;
+    float* kept = state + (size_t)slot * hidden;
+    const float* end = h + (size_t)last * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float c = cur[i];
+        const float p = kept[i];
+        kept[i] = end[i];
+        dst[i] = from_f32<O>(c + (p - c) * mu[i]);
+    }
+}
+
+template <typename O>
+static int token_shift_launch(const float* h, const float* mu, float* state, const int* request_of_token,
+                              const int* query_start, const int* slots, void* out, int rows, int hidden, int num_slots,
+                              cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0) return KIRAI_ERR_BAD_SIZE;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    return launch_pdl(token_shift_kernel<O>, dim3(rows), dim3(threads), 0, stream, 1u, h, mu, state, request_of_token,
+                      query_start, slots, (O*)out, hidden, num_slots);
+}
+
+KIRAI_EXPORT int kirai_token_shift_f32(const float* h, const float* mu, float* state, const int* request_of_token,
+                                       const int* query_start, const int* slots, void* out, int rows, int hidden,
+                                       int num_slots, cudaStream_t stream) {
+    return token_shift_launch<float>(h, mu, state, request_of_token, query_start, slots, out, rows, hidden, num_slots, stream);
+}
+KIRAI_EXPORT int kirai_token_shift_bf16(const float* h, const float* mu, float* state, const int* request_of_token,
+                                        const int* query_start, const int* slots, void* out, int rows, int hidden,
+                                        int num_slots, cudaStream_t stream) {
+    return token_shift_launch<bf16>(h, mu, state, request_of_token, query_start, slots, out, rows, hidden, num_slots, stream);
+}
+
+// ----------------------------------------------------------------------- minGRU
+// zxg [T, 3 W] (float32): the stacked product, columns [0, W) the gate's, [W, 2W) the candidate's, [2W, 3W) the
+// output gate's pre-activations.  z = sigmoid(. + zb); u = . + xb; c = u + 1/2 where u >= 0, sigmoid(u) below;
+// S <- (1 - z) S + z c; out = S * silu(g).
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ void mingru_terms(const float* __restrict__ row, int width, int ch, float zb, float xb, float& z, float& c) {
+    z = sigmoid_f32(row[ch] + zb);
+    const float u = row[width + ch] + xb;
+    c = u >= 0.0f ? u + 0.5f : sigmoid_f32(u);
+}
+
+// A thread per (request, channel) walks the request's tokens of this step in order.
+template <typename O>
+__global__ void mingru_walk_kernel(const float* __restrict__ zxg, long row_stride, const float* __restrict__ z_bias,
+                                   const float* __restrict__ x_bias, float* __restrict__ state,
+                                   const int* __restrict__ query_start, const int* __restrict__ slots, O* __restrict__ out,
+                                   int width, int num_slots) {
+    pdl_launch_dependents();
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    const int request = blockIdx.y;
+    const int first = query_start[request], end = query_start[request + 1];
+    const int slot = slots[request];
+    if (ch >= width || slot < 0 || slot >= num_slots) return;
+    const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
+    pdl_wait();
+    float s = state[(size_t)slot * width + ch];
+    for (int t = first; t < end; ++t) {
+        const float* row = zxg + (size_t)t * row_stride;
+        float z, c;
+        mingru_terms(row, width, ch, zb, xb, z, c);
+        s = fmaf(z, c - s, s);  // (1 - z) s + z c
+        const float g = row[2 * width + ch];
+        out[(size_t)t * width + ch] = from_f32<O>(s * g * sigmoid_f32(g));
+    }
+    state[(size_t)slot * width + ch] = s;
+}
+
+#define SCAN_PIECE 64
+
+// Pieces of SCAN_PIECE tokens, counted from the request's first row of this step.  Pass 1: a thread per (piece,
+// channel) leaves the piece's decay (product of 1 - z) and its end state from a zero start.
+__global__ void mingru_piece_kernel(const float* __restrict__ zxg, long row_stride, const float* __restrict__ z_bias,
+                                    const float* __restrict__ x_bias, const int* __restrict__ query_start,
+                                    float* __restrict__ decay, float* __restrict__ ends, int width, int max_pieces) {
+    pdl_launch_dependents();
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    const int piece = blockIdx.y, request = blockIdx.z;
+    const int first = query_start[request] + piece * SCAN_PIECE;
+    const int end = min(query_start[request + 1], first + SCAN_PIECE);
+    if (ch >= width || first >= end) return;
+    const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
+    pdl_wait();
+    float a = 1.0f, s = 0.0f;
+    for (int t = first; t < end; ++t) {
+        float z, c;
+        mingru_terms(zxg + (size_t)t * row_stride, width, ch, zb, xb, z, c);
+        a *= 1.0f - z;
+        s = fmaf(z, c - s, s);
+    }
+    const size_t at = ((size_t)request * max_pieces + piece) * width + ch;
+    decay[at] = a;
+    ends[at] = s;
+}
+
+// Pass 2: a thread per (request, channel) turns the pieces' end states into the state each piece starts from
+// (in place in `ends`) and leaves the request's new state in its slot.
+__global__ void mingru_carry_kernel(const float* __restrict__ decay, float* __restrict__ ends, float* __restrict__ state,
+                                    const int* __restrict__ query_start, const int* __restrict__ slots, int width,
+                                    int max_pieces, int num_slots) {
+    pdl_launch_dependents();
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    const int request = blockIdx.y;
+    const int tokens = query_start[request + 1] - query_start[request];
+    const int pieces = (tokens + SCAN_PIECE - 1) / SCAN_PIECE;
+    const int slot = slots[request];
+    if (ch >= width || slot < 0 || slot >= num_slots) return;
+    pdl_wait();
+    float s = state[(size_t)slot * width + ch];
+    for (int p = 0; p < pieces; ++p) {
+        const size_t at = ((size_t)request * max_pieces + p) * width + ch;
+        const float incoming = s;
+        s = fmaf(decay[at], s, ends[at]);
+        ends[at] = incoming;
+    }
+    state[(size_t)slot * width + ch] = s;
+}
+
+// Pass 3: a thread per (piece, channel) walks its piece again from the incoming state and writes the rows.
+template <typename O>
+__global__ void mingru_rows_kernel(const float* __restrict__ zxg, long row_stride, const float* __restrict__ z_bias,
+                                   const float* __restrict__ x_bias, const int* __restrict__ query_start,
+                                   const float* __restrict__ incoming, O* __restrict__ out, int width, int max_pieces) {
+    pdl_launch_dependents();
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    const int piece = blockIdx.y, request = blockIdx.z;
+    const int first = query_start[request] + piece * SCAN_PIECE;
+    const int end = min(query_start[request + 1], first + SCAN_PIECE);
+    if (ch >= width || first >= end) return;
+    const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
+    pdl_wait();
+    float s = incoming[((size_t)request * max_pieces + piece) * width + ch];
+    for (int t = first; t < end; ++t) {
+        const float* row = zxg + (size_t)t * row_stride;
+        float z, c;
+        mingru_terms(row, width, ch, zb, xb, z, c);
+        s = fmaf(z, c - s, s);
+        const float g = row[2 * width + ch];
+        out[(size_t)t * width + ch] = from_f32<O>(s * g * sigmoid_f32(g));
+    }
+}
+
+// scratch: 2 * requests * ceil(max_query_len / SCAN_PIECE) * width floats when max_query_len > walk_limit, else unused.
+template <typename O>
+static int mingru_launch(const float* zxg, long row_stride, const float* z_bias, const float* x_bias, float* state,
+                         const int* query_start, const int* slots, void* out, float* scratch, int requests,
+                         int max_query_len, int width, int num_slots, int walk_limit, cudaStream_t stream) {
+    if (requests <= 0 || max_query_len <= 0) return 0;
+    if (width <= 0 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
+    const int threads = 128;
+    const unsigned blocks = (unsigned)((width + threads - 1) / threads);
+    if (max_query_len <= walk_limit || !scratch) {
+        return launch_pdl(mingru_walk_kernel<O>, dim3(blocks, requests), dim3(threads), 0, stream, 1u, zxg, row_stride, z_bias,
+                          x_bias, state, query_start, slots, (O*)out, width, num_slots);
+    }
+    const int max_pieces = (max_query_len + SCAN_PIECE - 1) / SCAN_PIECE;
+    if (max_pieces > 65535) return KIRAI_ERR_BAD_SIZE;
+    float* decay = scratch;
+    float* ends = scratch + (size_t)requests * max_pieces * width;
+    int status = launch_pdl(mingru_piece_kernel, dim3(blocks, max_pieces, requests), dim3(threads), 0, stream, 1u, zxg, row_stride,
+                            z_bias, x_bias, query_start, decay, ends, width, max_pieces);
+    if (status) return status;
+    status = launch_pdl(mingru_carry_kernel, dim3(blocks, requests), dim3(threads), 0, stream, 1u, (const float*)decay, ends, state,
+                        query_start, slots, width, max_pieces, num_slots);
+    if (status) return status;
+    return launch_pdl(mingru_rows_kernel<O>, dim3(blocks, max_pieces, requests), dim3(threads), 0, stream, 1u, zxg, row_stride,
+                      z_bias, x_bias, query_start, (const float*)ends, (O*)out, width, max_pieces);
+}
+
+KIRAI_EXPORT int kirai_mingru_piece_tokens() { return SCAN_PIECE; }
+
+KIRAI_EXPORT int kirai_mingru_f32(const float* zxg, long row_stride, const float* z_bias, const float* x_bias, float* state,
+                                  const int* query_start, const int* slots, void* out, float* scratch, int requests,
+                                  int max_query_len, int width, int num_slots, int walk_limit, cudaStream_t stream) {
+    return mingru_launch<float>(zxg, row_stride, z_bias, x_bias, state, query_start, slots, out, scratch, requests,
+                                max_query_len, width, num_slots, walk_limit, stream);
+}
+KIRAI_EXPORT int kirai_mingru_bf16(const float* zxg, long row_stride, const float* z_bias, const float* x_bias, float* state,
+                                   const int* query_start, const int* slots, void* out, float* scratch, int requests,
+                                   int max_query_len, int width, int num_slots, int walk_limit, cudaStream_t stream) {
+    return mingru_launch<bf16>(zxg, row_stride, z_bias, x_bias, state, query_start, slots, out, scratch, requests,
+                               max_query_len, width, num_slots, walk_limit, stream);
+}
+
+// ------------------------------------- attention preparation: bias, rotation, factor
+// One block per token.  qkv row (float32): nq heads of dk, then nkv heads of dk, then nkv heads of dv (further
+// columns, as an output gate's, are not touched).  Columns [rot_off, rot_off + rot_dims) of every query and key head
+// are rotated, column i of the first half with column i + rot_dims / 2, by position * inv_freq[i]; query head h is
+// multiplied by q_factor[h].  Queries leave as [nq, dpad] rows with zeros beyond dk; keys and values go to the
+// token's row of its page, cache [pages, 2, nkv, page, dpad].
+template <typename T>
+__device__ __forceinline__ void rotate_head_to(const float* __restrict__ src, const float* __restrict__ bias, T* __restrict__ dst,
+                                               int width, int rot_off, int rot_dims, const float* __restrict__ inv_freq,
+                                               float pos, float factor, int lane, int lanes) {
+    const int half = rot_dims >> 1;
+    for (int c = lane; c < width; c += lanes) {
+        const int r = c - rot_off;
+        if (r >= 0 && r < rot_dims) {
+            if (r >= half) continue;  // written with its partner
+            const float u = src[c] + (bias ? bias[c] : 0.0f);
+            const float v = src[c + half] + (bias ? bias[c + half] : 0.0f);
+            float sn, cs;
+            sincosf(pos * inv_freq[r], &sn, &cs);
+            dst[c] = from_f32<T>((u * cs - v * sn) * factor);
+            dst[c + half] = from_f32<T>((v * cs + u * sn) * factor);
+        } else {
+            dst[c] = from_f32<T>((src[c] + (bias ? bias[c] : 0.0f)) * factor);
+        }
+    }
+}
+
+template <typename T>
+__global__ void qkv_rope_write_kernel(const float* __restrict__ qkv, long qkv_stride, const float* __restrict__ q_bias,
+                                      const float* __restrict__ k_bias, const float* __restrict__ v_bias,
+                                      const float* __restrict__ q_factor, const float* __restrict__ inv_freq, int rot_off,
+                                      int rot_dims, T* __restrict__ q_out, T* __restrict__ cache,
+                                      const int* __restrict__ block_table, const int* __restrict__ request_of_token,
+                                      const int* __restrict__ positions, int q_heads, int kv_heads, int dk, int dv, int dpad,
+                                      int page_size, int table_width, int num_pages, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    const int token = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int position = positions[token];
+    long page_base = -1;
+    if (kv_heads > 0) {
+        const int logical = position / page_size;
+        const int page = logical < table_width ? block_table[(long)request_of_token[token] * table_width + logical] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(error_flag, KIRAI_FLAG_NO_PAGE_WRITE);
+        } else {
+            page_base = (((long)page * 2) * kv_heads * page_size + (position % page_size)) * (long)dpad;
+        }
+    }
+    pdl_wait();
+    const float pos = (float)position;
+    const float* src = qkv + (size_t)token * qkv_stride;
+    const long head_rows = (long)page_size * dpad;
+    // a warp per head: query heads, then key heads, then value heads
+    for (int unit = warp; unit < q_heads + 2 * kv_heads; unit += warps) {
+        if (unit < q_heads) {
+            T* dst = q_out + ((size_t)token * q_heads + unit) * dpad;
+            rotate_head_to<T>(src + (size_t)unit * dk, q_bias ? q_bias + (size_t)unit * dk : nullptr, dst, dk, rot_off, rot_dims,
+                              inv_freq, pos, q_factor ? q_factor[unit] : 1.0f, lane, 32);
+            for (int c = dk + lane; c < dpad; c += 32) dst[c] = from_f32<T>(0.0f);
+        } else if (page_base >= 0 && unit < q_heads + kv_heads) {
+            const int head = unit - q_heads;
+            rotate_head_to<T>(src + (size_t)q_heads * dk + (size_t)head * dk, k_bias ? k_bias + (size_t)head * dk : nullptr,
+                              cache + page_base + head * head_rows, dk, rot_off, rot_dims, inv_freq, pos, 1.0f, lane, 32);
+        } else if (page_base >= 0) {
+            const int head = unit - q_heads - kv_heads;
+            const float* v = src + (size_t)(q_heads + kv_heads) * dk + (size_t)head * dv;
+            T* dst = cache + page_base + (long)kv_heads * head_rows + head * head_rows;
+            for (int c = lane; c < dv; c += 32) dst[c] = from_f32<T>(v[c] + (v_bias ? v_bias[(size_t)head * dv + c] : 0.0f));
+        }
+    }
+}
+
+template <typename T>
+static int qkv_rope_write_launch(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias, const float* v_bias,
+                                 const float* q_factor, const float* inv_freq, int rot_off, int rot_dims, void* q_out, void* cache,
+                                 const int* block_table, const int* request_of_token, const int* positions, int tokens,
+                                 int q_heads, int kv_heads, int dk, int dv, int dpad, int page_size, int table_width,
+                                 int num_pages, int* error_flag, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (q_heads <= 0 || kv_heads < 0 || dk <= 0 || dv <= 0 || dpad < dk || dpad < dv || page_size <= 0) return KIRAI_ERR_BAD_SIZE;
+    if (rot_dims < 0 || rot_dims % 2 || rot_off < 0 || rot_off + rot_dims > dk || (rot_dims > 0 && !inv_freq)) return KIRAI_ERR_BAD_SIZE;
+    if (kv_heads > 0 && !cache) return KIRAI_ERR_BAD_SIZE;
+    const int units = q_heads + 2 * kv_heads;
+    const int threads = units >= 8 ? 256 : 32 * units;
+    return launch_pdl(qkv_rope_write_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 1u, qkv, qkv_stride, q_bias, k_bias, v_bias,
+                      q_factor, inv_freq, rot_off, rot_dims, (T*)q_out, (T*)cache, block_table, request_of_token, positions,
+                      q_heads, kv_heads, dk, dv, dpad, page_size, table_width, num_pages, error_flag);
+}
+
+KIRAI_EXPORT int kirai_qkv_rope_write_f32(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias,
+                                          const float* v_bias, const float* q_factor, const float* inv_freq, int rot_off,
+                                          int rot_dims, void* q_out, void* cache, const int* block_table,
+                                          const int* request_of_token, const int* positions, int tokens, int q_heads,
+                                          int kv_heads, int dk, int dv, int dpad, int page_size, int table_width,
+                                          int num_pages, int* error_flag, cudaStream_t stream) {
+    return qkv_rope_write_launch<float>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_factor, inv_freq, rot_off, rot_dims, q_out,
+                                        cache, block_table, request_of_token, positions, tokens, q_heads, kv_heads, dk, dv, dpad,
+                                        page_size, table_width, num_pages, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_qkv_rope_write_bf16(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias,
+                                           const float* v_bias, const float* q_factor, const float* inv_freq, int rot_off,
+                                           int rot_dims, void* q_out, void* cache, const int* block_table,
+                                           const int* request_of_token, const int* positions, int tokens, int q_heads,
+                                           int kv_heads, int dk, int dv, int dpad, int page_size, int table_width,
+                                           int num_pages, int* error_flag, cudaStream_t stream) {
+    return qkv_rope_write_launch<bf16>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_factor, inv_freq, rot_off, rot_dims, q_out,
+                                       cache, block_table, request_of_token, positions, tokens, q_heads, kv_heads, dk, dv, dpad,
+                                       page_size, table_width, num_pages, error_flag, stream);
+}
+
+// --------------------------------------------------- latent attention preparation
+// One block per token.  down row (float32): q_rank columns of the query latent, kv_rank of the key/value latent,
+// rot_dims of the key part that all heads share.  Both latents are divided by their root mean square (eps inside
+// the root) and multiplied by a weight per column; the shared key part is rotated whole (column i with column
+// i + rot_dims / 2).  The query latent leaves as [q_rank] in the runtime dtype; the page row of the token gets
+// [latent, rotated part] as its key row and [latent] as its value row (cache [pages, 2, 1, page, dpad], the rest of
+// a row stays zero).
+template <typename T>
+__global__ void latent_prepare_kernel(const float* __restrict__ down, long down_stride, const float* __restrict__ q_weight,
+                                      const float* __restrict__ kv_weight, const float* __restrict__ inv_freq, float eps,
+                                      T* __restrict__ q_latent, T* __restrict__ cache, const int* __restrict__ block_table,
+                                      const int* __restrict__ request_of_token, const int* __restrict__ positions, int q_rank,
+                                      int kv_rank, int rot_dims, int dpad, int page_size, int table_width, int num_pages,
+                                      int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const int token = blockIdx.x;
+    const int position = positions[token];
+    long page_base = -1;
+    {
+        const int logical = position / page_size;
+        const int page = logical < table_width ? block_table[(long)request_of_token[token] * table_width + logical] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(error_flag, KIRAI_FLAG_NO_PAGE_WRITE);
+        } else {
+            page_base = (((long)page * 2) * page_size + (position % page_size)) * (long)dpad;
+        }
+    }
+    pdl_wait();
+    const float* src = down + (size_t)token * down_stride;
+    float q_acc = 0.0f, kv_acc = 0.0f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) q_acc = fmaf(src[i], src[i], q_acc);
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) kv_acc = fmaf(src[q_rank + i], src[q_rank + i], kv_acc);
+    const float q_var = q_rank > 0 ? block_sum(q_acc, scratch) / (float)q_rank + eps : 1.0f;
+    const float kv_var = block_sum(kv_acc, scratch) / (float)kv_rank + eps;
+    const float q_scale = q_var == 0.0f ? 0.0f : 1.0f / sqrtf(q_var);
+    const float kv_scale = kv_var == 0.0f ? 0.0f : 1.0f / sqrtf(kv_var);
+    T* q_dst = q_latent + (size_t)token * q_rank;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) q_dst[i] = from_f32<T>(src[i] * q_scale * q_weight[i]);
+    if (page_base < 0) return;
+    T* key = cache + page_base;
+    T* value = cache + page_base + (long)page_size * dpad;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
+        const T c = from_f32<T>(src[q_rank + i] * kv_scale * kv_weight[i]);
+        key[i] = c;
+        value[i] = c;
+    }
+    const int half = rot_dims >> 1;
+    const float pos = (float)position;
+    const float* shared_part = src + q_rank + kv_rank;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float u = shared_part[i], v = shared_part[i + half];
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        key[kv_rank + i] = from_f32<T>(u * cs - v * sn);
+        key[kv_rank + i + half] = from_f32<T>(v * cs + u * sn);
+    }
+}
+
+template <typename T>
+static int latent_prepare_launch(const float* down, long down_stride, const float* q_weight, const float* kv_weight,
+                                 const float* inv_freq, float eps, void* q_latent, void* cache, const int* block_table,
+                                 const int* request_of_token, const int* positions, int tokens, int q_rank, int kv_rank,
+                                 int rot_dims, int dpad, int page_size, int table_width, int num_pages, int* error_flag,
+                                 cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (q_rank < 0 || kv_rank <= 0 || rot_dims < 0 || rot_dims % 2 || dpad < kv_rank + rot_dims || page_size <= 0 || !cache)
+        return KIRAI_ERR_BAD_SIZE;
+    const int threads = (q_rank + kv_rank) >= 1024 ? 256 : 128;
+    return launch_pdl(latent_prepare_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 1u, down, down_stride, q_weight, kv_weight,
+                      inv_freq, eps, (T*)q_latent, (T*)cache, block_table, request_of_token, positions, q_rank, kv_rank, rot_dims,
+                      dpad, page_size, table_width, num_pages, error_flag);
+}
+
+KIRAI_EXPORT int kirai_latent_prepare_f32(const float* down, long down_stride, const float* q_weight, const float* kv_weight,
+                                          const float* inv_freq, float eps, void* q_latent, void* cache, const int* block_table,
+                                          const int* request_of_token, const int* positions, int tokens, int q_rank,
+                                          int kv_rank, int rot_dims, int dpad, int page_size, int table_width, int num_pages,
+                                          int* error_flag, cudaStream_t stream) {
+    return latent_prepare_launch<float>(down, down_stride, q_weight, kv_weight, inv_freq, eps, q_latent, cache, block_table,
+                                        request_of_token, positions, tokens, q_rank, kv_rank, rot_dims, dpad, page_size,
+                                        table_width, num_pages, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_latent_prepare_bf16(const float* down, long down_stride, const float* q_weight, const float* kv_weight,
+                                           const float* inv_freq, float eps, void* q_latent, void* cache, const int* block_table,
+                                           const int* request_of_token, const int* positions, int tokens, int q_rank,
+                                           int kv_rank, int rot_dims, int dpad, int page_size, int table_width, int num_pages,
+                                           int* error_flag, cudaStream_t stream) {
+    return latent_prepare_launch<bf16>(down, down_stride, q_weight, kv_weight, inv_freq, eps, q_latent, cache, block_table,
+                                       request_of_token, positions, tokens, q_rank, kv_rank, rot_dims, dpad, page_size,
+                                       table_width, num_pages, error_flag, stream);
+}
+
+// ------------------------------------------------------------- element-wise steps
+// x [T, heads, dpad] (in place) *= sigmoid(gate[T, heads * used]) on the first `used` columns of every head; gate is
+// a run of columns of a 32-bit product (row stride gate_stride).
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, const float* __restrict__ gate, long gate_stride, long rows, int heads,
+                                    int used, int dpad) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long per_row = (long)heads * used;
+    const long total = rows * per_row;
+    for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
+        const long row = at / per_row;
+        const int col = (int)(at - row * per_row);
+        const int head = col / used, c = col - head * used;
+        T* p = x + (row * heads + head) * dpad + c;
+        *p = from_f32<T>(to_f32<T>(*p) * sigmoid_f32(gate[row * gate_stride + col]));
+    }
+}
+
+template <typename T>
+static int sigmoid_gate_launch(void* x, const float* gate, long gate_stride, int rows, int heads, int used, int dpad,
+                               cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (heads <= 0 || used <= 0 || dpad < used) return KIRAI_ERR_BAD_SIZE;
+    const long total = (long)rows * heads * used;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)min((total + threads - 1) / threads, (long)148 * 16);
+    return launch_pdl(sigmoid_gate_kernel<T>, dim3(blocks), dim3(threads), 0, stream, 1u, (T*)x, gate, gate_stride, (long)rows, heads,
+                      used, dpad);
+}
+
+KIRAI_EXPORT int kirai_sigmoid_gate_f32(void* x, const float* gate, long gate_stride, int rows, int heads, int used, int dpad,
+                                        cudaStream_t stream) {
+    return sigmoid_gate_launch<float>(x, gate, gate_stride, rows, heads, used, dpad, stream);
+}
+KIRAI_EXPORT int kirai_sigmoid_gate_bf16(void* x, const float* gate, long gate_stride, int rows, int heads, int used, int dpad,
+                                         cudaStream_t stream) {
+    return sigmoid_gate_launch<bf16>(x, gate, gate_stride, rows, heads, used, dpad, stream);
+}
+
+// out [T, I] = act(gate) * up for gate_up [T, 2 I] (gate half first); act 0: silu, 1: the tanh form of gelu,
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long rows, int inter, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long total = rows * inter;
+    for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
+        const long row = at / inter;
+        const int c = (int)(at - row * inter);
+        const float g = to_f32<T>(gate_up[row * 2 * inter + c]);
+        const float u = to_f32<T>(gate_up[row * 2 * inter + inter + c]);
+        const float a = act == 1 ? gelu_tanh_f32(g) : g * sigmoid_f32(g);
+        out[at] = from_f32<T>(a * u);
+    }
+}
+
+template <typename T>
+static int gated_activation_launch(const void* gate_up, void* out, int rows, int inter, int act, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (inter <= 0 || act < 0 || act > 1) return KIRAI_ERR_BAD_SIZE;
+    const long total = (long)rows * inter;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)min((total + threads - 1) / threads, (long)148 * 16);
+    return launch_pdl(gated_activation_kernel<T>, dim3(blocks), dim3(threads), 0, stream, 1u, (const T*)gate_up, (T*)out, (long)rows,
+                      inter, act);
+}
+
+KIRAI_EXPORT int kirai_gated_activation_f32(const void* gate_up, void* out, int rows, int inter, int act, cudaStream_t stream) {
+    return gated_activation_launch<float>(gate_up, out, rows, inter, act, stream);
+}
+KIRAI_EXPORT int kirai_gated_activation_bf16(const void* gate_up, void* out, int rows, int inter, int act, cudaStream_t stream) {
+    return gated_activation_launch<bf16>(gate_up, out, rows, inter, act, stream);
+}
+
+// x [T, width] (in place) += bias [width] (float32).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, long rows, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long total = rows * width;
+    for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x)
+        x[at] = from_f32<T>(to_f32<T>(x[at]) + bias[at % width]);
+}
+
+template <typename T>
+static int add_bias_launch(void* x, const float* bias, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return KIRAI_ERR_BAD_SIZE;
+    const long total = (long)rows * width;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)min((total + threads - 1) / threads, (long)148 * 16);
+    return launch_pdl(add_bias_kernel<T>, dim3(blocks), dim3(threads), 0, stream, 1u, (T*)x, bias, (long)rows, width);
+}
+
+KIRAI_EXPORT int kirai_add_bias_f32(void* x, const float* bias, int rows, int width, cudaStream_t stream) {
+    return add_bias_launch<float>(x, bias, rows, width, stream);
+}
+KIRAI_EXPORT int kirai_add_bias_bf16(void* x, const float* bias, int rows, int width, cudaStream_t stream) {
+    return add_bias_launch<bf16>(x, bias, rows, width, stream);
+}

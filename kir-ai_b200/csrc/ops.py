@@ -347,6 +347,162 @@ def qkv_wide_norm_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim:
     return q_out
 
 
+# ------------------------------------------------ layer norm, token shift, recurrences
+def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                  out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None, delta_bias: Optional[torch.Tensor] = None,
+                  wide: bool = False) -> torch.Tensor:
+    """``resid += delta + delta_bias`` (32-bit, in place), then the layer norm with a weight and no bias of the sum:
+    (x - mean) / sqrt(var + eps) * weight, in ``out_dtype`` (``wide``: in 32-bit whatever the runtime dtype, for a
+    step that goes on in 32-bit).  With ``row_index`` only those rows are produced and the stream is left as it is."""
+    _need_cuda(resid, delta, weight, row_index, delta_bias)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    hidden = resid.shape[1]
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == hidden
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.dtype == out_dtype and delta.is_contiguous()
+    if delta_bias is not None:
+        assert delta_bias.dtype == torch.float32 and delta_bias.numel() == hidden and delta_bias.is_contiguous()
+    if row_index is not None:
+        assert row_index.dtype == torch.int32 and row_index.is_contiguous()
+    rows = resid.shape[0] if row_index is None else row_index.numel()
+    out = torch.empty((rows, hidden), dtype=torch.float32 if wide else out_dtype, device=resid.device)
+    _call(f"kirai_add_layernorm_{_suffix(out_dtype)}", _ptr(resid), _ptr(delta), _ptr(delta_bias), _ptr(weight), _ptr(out),
+          _ptr(row_index), _i(rows), _i(hidden), _f(eps), _i(1 if wide else 0), _stream())
+    return out
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, batch, out_dtype: torch.dtype) -> torch.Tensor:
+    """Rows ``h`` [T, H] (float32) mixed with the row of the token before: h_t + (h_{t-1} - h_t) * mu.  The row before
+    a request's first row of this step is the request's slot of ``state`` [slots, H] (float32), which afterwards holds
+    the request's last row of this step."""
+    _need_cuda(h, mu, state)
+    assert h.dtype == torch.float32 and h.dim() == 2 and h.is_contiguous()
+    assert mu.dtype == torch.float32 and mu.numel() == h.shape[1] and mu.is_contiguous()
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == h.shape[1] and state.is_contiguous()
+    out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
+    _call(f"kirai_token_shift_{_suffix(out_dtype)}", _ptr(h), _ptr(mu), _ptr(state), _ptr(batch.request_of_token),
+          _ptr(batch.query_start), _ptr(batch.slots), _ptr(out), _i(h.shape[0]), _i(h.shape[1]), _i(state.shape[0]), _stream())
+    return out
+
+
+MINGRU_WALK_LIMIT = 16  # steps whose longest run of tokens is at most this walk it; longer runs are scanned in pieces
+
+
+def mingru(zxg: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor], state: torch.Tensor, batch,
+           out_dtype: torch.dtype, walk_limit: Optional[int] = None) -> torch.Tensor:
+    """The minGRU recurrence over each request's tokens of this step.  ``zxg`` [T, 3 W] (float32): pre-activations of
+    the gate z, the candidate and the output gate.  z = sigmoid(. + z_bias); u = . + x_bias; candidate u + 1/2 where
+    u >= 0 and sigmoid(u) below; S <- (1 - z) S + z candidate, from the request's slot of ``state`` [slots, W]
+    (float32), which afterwards holds the last S; returns S * silu(g) as [T, W] in ``out_dtype``."""
+    _need_cuda(zxg, z_bias, x_bias, state)
+    assert zxg.dtype == torch.float32 and zxg.dim() == 2 and zxg.stride(1) == 1 and zxg.shape[1] % 3 == 0
+    width = zxg.shape[1] // 3
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == width and state.is_contiguous()
+    for bias in (z_bias, x_bias):
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == width and bias.is_contiguous())
+    walk_limit = MINGRU_WALK_LIMIT if walk_limit is None else walk_limit
+    out = torch.empty((zxg.shape[0], width), dtype=out_dtype, device=zxg.device)
+    scratch = None
+    if batch.max_query_len > walk_limit:
+        fn = library().kirai_mingru_piece_tokens
+        fn.restype = ctypes.c_int
+        pieces = -(-batch.max_query_len // int(fn()))
+        scratch = torch.empty((2, batch.num_requests, pieces, width), dtype=torch.float32, device=zxg.device)
+    _call(f"kirai_mingru_{_suffix(out_dtype)}", _ptr(zxg), _l(zxg.stride(0)), _ptr(z_bias), _ptr(x_bias), _ptr(state),
+          _ptr(batch.query_start), _ptr(batch.slots), _ptr(out), _ptr(scratch), _i(batch.num_requests),
+          _i(batch.max_query_len), _i(width), _i(state.shape[0]), _i(walk_limit), _stream())
+    return out
+
+
+def qkv_rope_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim: int, value_dim: int, pad_dim: int,
+                   q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor], v_bias: Optional[torch.Tensor],
+                   q_factor: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rot_offset: int, rot_dims: int,
+                   cache: Optional[torch.Tensor], block_table: torch.Tensor, request_of_token: torch.Tensor,
+                   positions: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Prepares attention whose projections carry biases and whose heads are rotated in part: ``qkv`` [T, >= nq dk +
+    nkv dk + nkv dv] (float32, the stacked product; further columns are left alone; ``kv_heads`` 0 for queries only)
+    gets its biases, columns [rot_offset, rot_offset + rot_dims) of every query and key head are rotated (column i of
+    the first half with column i + rot_dims / 2, by position * inv_freq[i]), query head h is multiplied by
+    ``q_factor[h]``, keys and values go to the token's page row in ``cache`` [pages, 2, nkv, page, pad_dim], and the
+    queries come back as [T, nq, pad_dim] in ``out_dtype`` with zero columns beyond dk."""
+    _need_cuda(qkv, q_bias, k_bias, v_bias, q_factor, inv_freq, cache, block_table, request_of_token, positions)
+    assert qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.stride(1) == 1
+    assert qkv.shape[1] >= q_heads * key_dim + kv_heads * (key_dim + value_dim)
+    for t, n in ((q_bias, q_heads * key_dim), (k_bias, kv_heads * key_dim), (v_bias, kv_heads * value_dim),
+                 (q_factor, q_heads), (inv_freq, rot_dims // 2)):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == n and t.is_contiguous())
+    num_pages, page_size = 0, 1
+    if kv_heads:
+        num_pages, c_heads, page_size, c_dim = _cache_dims(cache)
+        assert (c_heads, c_dim) == (kv_heads, pad_dim) and cache.dtype == out_dtype
+    tokens = qkv.shape[0]
+    q_out = torch.empty((tokens, q_heads, pad_dim), dtype=out_dtype, device=qkv.device)
+    _call(f"kirai_qkv_rope_write_{_suffix(out_dtype)}", _ptr(qkv), _l(qkv.stride(0)), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+          _ptr(q_factor), _ptr(inv_freq if rot_dims else None), _i(rot_offset), _i(rot_dims), _ptr(q_out),
+          _ptr(cache if kv_heads else None), _ptr(block_table), _ptr(request_of_token), _ptr(positions), _i(tokens),
+          _i(q_heads), _i(kv_heads), _i(key_dim), _i(value_dim), _i(pad_dim), _i(page_size), _i(block_table.shape[1]),
+          _i(num_pages), _ptr(error_flag(qkv.device)), _stream())
+    return q_out
+
+
+def latent_prepare(down: torch.Tensor, q_rank: int, kv_rank: int, rot_dims: int, q_weight: Optional[torch.Tensor],
+                   kv_weight: torch.Tensor, inv_freq: Optional[torch.Tensor], eps: float, cache: torch.Tensor,
+                   block_table: torch.Tensor, request_of_token: torch.Tensor, positions: torch.Tensor,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """Prepares latent attention from ``down`` [T, q_rank + kv_rank + rot_dims] (float32, the stacked down
+    projections): both latents get their RMS norm (a weight per column, ``eps`` inside the root), the last
+    ``rot_dims`` columns, the key part that all heads share, are rotated whole by position * inv_freq, and the token's
+    page row in ``cache`` [pages, 2, 1, page, pad] gets [latent, rotated part] as its key row and [latent] as its value
+    row.  Returns the normed query latent [T, q_rank] in ``out_dtype``."""
+    _need_cuda(down, q_weight, kv_weight, inv_freq, cache, block_table, request_of_token, positions)
+    assert down.dtype == torch.float32 and down.dim() == 2 and down.stride(1) == 1 and down.shape[1] == q_rank + kv_rank + rot_dims
+    for t, n in ((q_weight, q_rank), (kv_weight, kv_rank), (inv_freq, rot_dims // 2)):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == n and t.is_contiguous())
+    num_pages, c_heads, page_size, pad_dim = _cache_dims(cache)
+    assert c_heads == 1 and pad_dim >= kv_rank + rot_dims and cache.dtype == out_dtype
+    tokens = down.shape[0]
+    q_latent = torch.empty((tokens, q_rank), dtype=out_dtype, device=down.device)
+    _call(f"kirai_latent_prepare_{_suffix(out_dtype)}", _ptr(down), _l(down.stride(0)), _ptr(q_weight), _ptr(kv_weight),
+          _ptr(inv_freq if rot_dims else None), _f(eps), _ptr(q_latent), _ptr(cache), _ptr(block_table), _ptr(request_of_token),
+          _ptr(positions), _i(tokens), _i(q_rank), _i(kv_rank), _i(rot_dims), _i(pad_dim), _i(page_size),
+          _i(block_table.shape[1]), _i(num_pages), _ptr(error_flag(down.device)), _stream())
+    return q_latent
+
+
+def sigmoid_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, used: int, pad_dim: int) -> torch.Tensor:
+    """``x`` [T, heads * pad_dim] (in place): the first ``used`` columns of every head times sigmoid of ``gate``
+    [T, heads * used] (float32; a run of columns of a wider product is allowed)."""
+    _need_cuda(x, gate)
+    assert x.dim() == 2 and x.is_contiguous() and x.shape[1] == heads * pad_dim
+    assert gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == (x.shape[0], heads * used)
+    _call(f"kirai_sigmoid_gate_{_suffix(x.dtype)}", _ptr(x), _ptr(gate), _l(gate.stride(0)), _i(x.shape[0]), _i(heads),
+          _i(used), _i(pad_dim), _stream())
+    return x
+
+
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_activation(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
+    """act(gate) * up for ``gate_up`` [T, 2 I] (gate half first); ``activation`` is ``silu`` or ``gelu_tanh``
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))).  Returns [T, I]."""
+    _need_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _call(f"kirai_gated_activation_{_suffix(gate_up.dtype)}", _ptr(gate_up), _ptr(out), _i(rows), _i(inter),
+          _i(GATED_ACTIVATIONS[activation]), _stream())
+    return out
+
+
+def add_bias_(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``x`` [T, W] (in place) += ``bias`` [W] (float32)."""
+    _need_cuda(x, bias)
+    assert x.dim() == 2 and x.is_contiguous() and bias.dtype == torch.float32 and bias.numel() == x.shape[1] and bias.is_contiguous()
+    _call(f"kirai_add_bias_{_suffix(x.dtype)}", _ptr(x), _ptr(bias), _i(x.shape[0]), _i(x.shape[1]), _stream())
+    return x
+
+
 _arrival_counters: dict = {}
 
 
@@ -534,18 +690,35 @@ def qk_norm_rope_kv_write_(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_
 
 
 # --------------------------------------------------------------------- attention
+def mask_code(window: Optional[int], chunk: Optional[int] = None) -> int:
+    """How the kernels are told which keys a query sees: 0 every key up to its own position, W > 0 the last W of
+    them, -C < 0 those of its own chunk of C positions (chunks counted from position 0 of the sequence)."""
+    if window and chunk:
+        raise KernelError("a layer has a window or a chunked mask, not both")
+    return -int(chunk) if chunk else int(window or 0)
+
+
+def _capped(name: str, softcap: Optional[float]):
+    """The entry point ``name`` or its form with a soft cap on the scores, and that form's extra argument."""
+    if softcap:
+        return name.replace("_bf16", "_softcap_bf16").replace("_f32", "_softcap_f32"), (_f(softcap),)
+    return name, ()
+
+
 def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                           request_of_token: torch.Tensor, positions: torch.Tensor, window: Optional[int],
-                          scale: float) -> torch.Tensor:
-    """Causal grouped-query attention of ``q`` [T, nq, d] over the paged cache; returns [T, nq * d]."""
+                          scale: float, chunk: Optional[int] = None, softcap: Optional[float] = None) -> torch.Tensor:
+    """Causal grouped-query attention of ``q`` [T, nq, d] over the paged cache; returns [T, nq * d].  ``chunk``: a
+    query sees the keys of its own chunk of that many positions only; ``softcap`` c: scores become c tanh(score / c)."""
     _need_cuda(q, cache, block_table, request_of_token, positions)
     num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
     rows, q_heads, qd, q_stride = _head_view(q)
     assert qd == head_dim and q.dtype == cache.dtype
     out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
-    _call(f"kirai_paged_attention_plain_{_suffix(q.dtype)}", _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table),
+    name, cap = _capped(f"kirai_paged_attention_plain_{_suffix(q.dtype)}", softcap)
+    _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table),
           _ptr(request_of_token), _ptr(positions), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride),
-          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale),
+          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap,
           _ptr(error_flag(q.device)), _stream())
     return out
 
@@ -582,7 +755,8 @@ def attention_prefill_takes_tcgen05(q_heads: int, kv_heads: int, head_dim: int, 
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, query_start: torch.Tensor,
                       context_len: torch.Tensor, max_query_len: int, window: Optional[int], scale: float,
-                      tcgen05: Optional[bool] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      tcgen05: Optional[bool] = None, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                      softcap: Optional[float] = None) -> torch.Tensor:
     """bf16 tensor-core attention for runs of new tokens (prompt portions, or any mix): q [T, nq, d].
     ``query_start`` holds rows of ``q`` and of the result, so the requests given may be a part of a larger batch
     (``out`` is then the whole batch's result, of which only their rows are written).  ``tcgen05`` picks the kernel (None: the tcgen05 kernel where it takes the shape, else the
@@ -598,10 +772,11 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     if out is None:
         out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
     assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
-    _call("kirai_attention_prefill_tc_bf16" if tcgen05 else "kirai_attention_prefill_bf16", _ptr(q), _ptr(cache), _ptr(out),
+    name, cap = _capped("kirai_attention_prefill_tc_bf16" if tcgen05 else "kirai_attention_prefill_bf16", softcap)
+    _call(name, _ptr(q), _ptr(cache), _ptr(out),
           _ptr(block_table), _ptr(query_start), _ptr(context_len), _i(requests), _i(max_query_len), _i(q_heads), _i(kv_heads),
-          _i(head_dim), _l(q_stride), _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale),
-          _ptr(error_flag(q.device)), _stream())
+          _i(head_dim), _l(q_stride), _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale),
+          *cap, _ptr(error_flag(q.device)), _stream())
     return out
 
 
@@ -694,7 +869,8 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
 
 
 def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
-                     window: Optional[int], scale: float, num_splits: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     window: Optional[int], scale: float, num_splits: int = 1, out: Optional[torch.Tensor] = None,
+                     chunk: Optional[int] = None, softcap: Optional[float] = None) -> torch.Tensor:
     """bf16 tensor-core attention for a batch in which every request brings one token: q [R, nq, d] (row r of ``q``,
     of the tables and of the result belongs to request r; ``out`` may be the head of a larger result)."""
     _need_cuda(q, cache, block_table, context_len)
@@ -709,9 +885,10 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
     if num_splits > 1 and not decode_pair_merges(rows * kv_heads, num_splits, head_dim, decode_cluster_room(q.device, head_dim, q_heads // kv_heads), q_heads // kv_heads):
         # the ranges' results go through a buffer and a second kernel
         partial = torch.empty((rows, q_heads, num_splits, head_dim + 2), dtype=torch.float32, device=q.device)
-    _call("kirai_attention_decode_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
+    name, cap = _capped("kirai_attention_decode_bf16", softcap)
+    _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
-          _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale), _i(num_splits),
+          _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap, _i(num_splits),
           _ptr(error_flag(q.device)), _stream())
     return out
 
@@ -728,7 +905,8 @@ def sm_count(device: torch.device) -> int:
 
 def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
                               window: Optional[int], scale: float, ctas: Optional[int] = None,
-                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                              softcap: Optional[float] = None) -> torch.Tensor:
     """The decode attention with the key tiles of all (request, kv head) pairs cut into ``ctas`` equal ranges
     (default: one per SM), so that every CTA reads the same number of keys whatever the batch looks like."""
     _need_cuda(q, cache, block_table, context_len)
@@ -741,15 +919,16 @@ def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table:
         out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
     assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=q.device)
-    _call("kirai_attention_decode_balanced_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
+    name, cap = _capped("kirai_attention_decode_balanced_bf16", softcap)
+    _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
-          _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale), _i(ctas),
+          _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap, _i(ctas),
           _ptr(error_flag(q.device)), _stream())
     return out
 
 
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, batch, window: Optional[int],
-                    scale: float) -> torch.Tensor:
+                    scale: float, chunk: Optional[int] = None, softcap: Optional[float] = None) -> torch.Tensor:
     """Attention of the product path over the paged cache for the tokens of ``batch``
     (a kirai_b200.engine.batch.StepBatch).  float32 takes the plain kernel; bfloat16 takes the
     tensor-core kernels (the decode kernel when every request brings one token), or the plain
@@ -757,24 +936,32 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     head_dim, q_heads, kv_heads = q.shape[2], q.shape[1], cache.shape[2]
     fast = attention_takes_tensor_cores(q.dtype, head_dim) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
     if not fast:
-        return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale)
+        return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale,
+                                     chunk, softcap)
     decode_rows = batch.num_requests if batch.decode_only else getattr(batch, "num_decode", 0)
     if decode_rows and q_heads // kv_heads <= 16:
         # The requests that bring one token stand first in the batch (the batch builder puts them there) and take the
         # decode kernels, which split a long context over many CTAs; prompt portions take the prompt kernel, and both
         # write their rows of one result.  A prompt kernel alone would give a decoding request one CTA per kv head.
         out = torch.empty((q.shape[0], q_heads * head_dim), dtype=q.dtype, device=q.device)
-        _decode_rows(q[:decode_rows], cache, block_table[:decode_rows], batch, decode_rows, window, scale, out[:decode_rows])
+        _decode_rows(q[:decode_rows], cache, block_table[:decode_rows], batch, decode_rows, window, scale, out[:decode_rows],
+                     chunk, softcap)
         if decode_rows < batch.num_requests:
             attention_prefill(q, cache, block_table[decode_rows:], batch.query_start[decode_rows:], batch.context_len[decode_rows:],
-                              batch.max_query_len, window, scale, out=out)
+                              batch.max_query_len, window, scale, out=out, chunk=chunk, softcap=softcap)
         return out
-    return attention_prefill(q, cache, block_table, batch.query_start, batch.context_len, batch.max_query_len, window, scale)
+    return attention_prefill(q, cache, block_table, batch.query_start, batch.context_len, batch.max_query_len, window, scale,
+                             chunk=chunk, softcap=softcap)
 
 
-def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int], scale: float, out: torch.Tensor) -> None:
+def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int], scale: float, out: torch.Tensor,
+                 chunk: Optional[int] = None, softcap: Optional[float] = None) -> None:
     """The decode attention of the first ``rows`` requests of ``batch`` (one token each)."""
     kv_heads = cache.shape[2]
+    mask = dict(chunk=chunk, softcap=softcap)
+    if chunk:
+        window = None
+    reach = window or chunk  # the most keys a token sees: what the launch is planned for
     room = decode_cluster_room(q.device, q.shape[2], q.shape[1] // kv_heads)
     context_len = batch.context_len[:rows]
     # the batch may say which kernel (a captured step does: its lengths change between replays); otherwise
@@ -783,19 +970,19 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
     longest = batch.max_context_len
     if balanced is None:
         lens = [start + count for start, count in zip(batch.start_positions[:rows], batch.query_lens[:rows])]
-        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device), room=room, head_dim=q.shape[2],
+        balanced, _ = decode_plan(lens, kv_heads, reach, sms=sm_count(q.device), room=room, head_dim=q.shape[2],
                                   group=q.shape[1] // kv_heads)
         longest = max(lens)
     forced = os.environ.get("KIRAI_DECODE_BALANCED")
     if forced in ("0", "1"):
         balanced = forced == "1"
     if balanced and rows <= 1024:
-        attention_decode_balanced(q, cache, block_table, context_len, window, scale, out=out)
+        attention_decode_balanced(q, cache, block_table, context_len, window, scale, out=out, **mask)
         return
     # (a captured step says how many ranges, planned for its requests' lengths; else the longest context decides)
-    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device),
+    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, reach or longest), sms=sm_count(q.device),
                                                                     room=room, head_dim=q.shape[2], group=q.shape[1] // kv_heads)
-    attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out)
+    attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out, **mask)
 
 
 def decode_prepares_qk(qkv: torch.Tensor, cache: Optional[torch.Tensor], batch, q_heads: int, kv_heads: int, head_dim: int) -> bool:

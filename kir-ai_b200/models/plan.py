@@ -24,11 +24,13 @@ from ..parts.embedding import Embedding, OutputHead
 @dataclass(frozen=True)
 class LayerCall:
     """Run ``block`` with cache layer ``cache`` (None: the mixer keeps nothing);
-    ``write`` false reads what an earlier call wrote in the same step."""
+    ``write`` false reads what an earlier call wrote in the same step.  ``shift_cache`` is the cache layer of the
+    block's token shift, where it has one (a state slot per request; every call has its own)."""
 
     block: int
     cache: Optional[int] = None
     write: bool = True
+    shift_cache: Optional[int] = None
 
 
 class PlanError(ValueError):
@@ -54,6 +56,13 @@ class ModelPlan:
         for step, call in enumerate(self.order):
             if not 0 <= call.block < len(self.blocks):
                 raise PlanError(f"order[{step}] names block {call.block}, but there are {len(self.blocks)} blocks")
+            shift_need = getattr(self.blocks[call.block], "shift_need", lambda: None)()
+            if (shift_need is None) != (call.shift_cache is None):
+                raise PlanError(f"order[{step}]: block {call.block} {'needs' if shift_need is not None else 'has no use for'} a cache layer for its token shift")
+            if shift_need is not None:
+                if call.shift_cache in needs:
+                    raise PlanError(f"order[{step}]: cache layer {call.shift_cache} is written by two calls")
+                needs[call.shift_cache] = shift_need
             need = self.blocks[call.block].mixer.cache_need()
             if need is None:
                 if call.cache is not None:
@@ -133,7 +142,11 @@ class DecoderModel:
                 following = self.plan.blocks[order[i + 1].block] if i + 1 < len(order) else None
                 if nvtx:
                     nvtx.range_push(f"layer call {i}: block {call.block}, {batch.num_tokens} tokens")
-                resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write, following)
+                if call.shift_cache is not None:
+                    resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write, following,
+                                                                        shift_cache=cache.layer_view(call.shift_cache))
+                else:
+                    resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write, following)
                 if nvtx:
                     nvtx.range_pop()
         return resid, delta

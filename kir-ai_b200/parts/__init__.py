@@ -4,10 +4,14 @@ from .base import (FeedForward, KVCacheNeed, Mixer, Norm, Part, PositionEncoding
 from .block import Block
 from .embedding import Embedding, OutputHead
 from .experts import RoutedExperts
+from .latent import LatentAttention
 from .linear import Linear
-from .norm import RMSNorm
+from .mingru import MinGRU
+from .norm import LayerNorm, RMSNorm
 from .rope import RotaryEmbedding
-from .swiglu import SwiGLU
+from .shift import TokenShift
+from .swiglu import GatedMLP, SwiGLU
 
 __all__ = ["GQAttention", "FeedForward", "KVCacheNeed", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime",
-           "StateNeed", "StreamCopy", "WeightSpec", "RoutedExperts", "Block", "Embedding", "OutputHead", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLU"]
+           "StateNeed", "StreamCopy", "WeightSpec", "RoutedExperts", "Block", "Embedding", "OutputHead", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLU",
+           "GatedMLP", "LatentAttention", "LayerNorm", "MinGRU", "TokenShift"]

@@ -26,6 +26,15 @@ kernels; cache rows are max(head_dim, value_dim) wide, rounded up to 8, the
 unused columns zero, and the output projection's matrix gets zero columns where
 a head's output is padding.  ``out_dtype`` is the dtype of the mixer's result
 (default: the runtime's).
+
+Further options, again constructor arguments.  With biases or a value width of its own and NO norm over the
+projection the layer may have a ``RotaryEmbedding`` (any part of a head, any frequency table): a second preparation
+kernel adds the biases, rotates, and writes queries, keys and values.  ``head_factor`` names a tensor [q_heads] by
+which each head's scores are multiplied (folded into the queries in 32-bit before they are rounded); ``softcap`` c
+turns a score s into c tanh(s / c) before the softmax; ``chunk`` C lets position i see j <= i only when both lie in
+the same run of C positions counted from the sequence's start (all keys stay cached); ``gate`` names a matrix
+[q_heads * value_dim, hidden]: the concatenated heads are multiplied by sigmoid(gate x) before the output
+projection (the matrix rides in the stacked q, k, v product); ``out_bias`` names a bias of the output projection.
 """
 from __future__ import annotations
 
@@ -43,7 +52,9 @@ class GQAttention(Mixer):
                  position: Optional[PositionEncoding], *, window: Optional[int] = None,
                  qk_norm_eps: Optional[float] = None, scale: Optional[float] = None, reads_only: bool = False,
                  names: Optional[Dict[str, str]] = None, value_dim: Optional[int] = None, bias: bool = False,
-                 qk_norm_over: str = "head", out_dtype: Optional[torch.dtype] = None):
+                 qk_norm_over: str = "head", out_dtype: Optional[torch.dtype] = None, head_factor: Optional[str] = None,
+                 softcap: Optional[float] = None, chunk: Optional[int] = None, gate: Optional[str] = None,
+                 out_bias: Optional[str] = None):
         if q_heads % kv_heads:
             raise ValueError(f"{q_heads} query heads are not a multiple of {kv_heads} kv heads")
         if qk_norm_over not in ("head", "projection"):
@@ -63,19 +74,37 @@ class GQAttention(Mixer):
         self.bias = bias
         self.out_dtype = out_dtype
         # the preparation that takes biases, a norm over the whole projection and values of their own width
-        self.wide = bias or self.value_dim != head_dim or (qk_norm_eps is not None and qk_norm_over == "projection")
+        self.softcap = float(softcap) if softcap else None
+        self.chunk = int(chunk) if chunk else None
+        if self.chunk and window:
+            raise ValueError("a layer has a window or a chunked mask, not both")
+        if (self.softcap or self.chunk) and reads_only:
+            raise ValueError("a soft cap or a chunked mask is not built for a layer that reads another layer's cache")
+        self.head_factor_name = prefix + head_factor if head_factor else None
+        self.gate_name = prefix + gate if gate else None
+        self.out_bias_name = prefix + out_bias if out_bias else None
+        self.head_factor = self.out_bias = None
+        self.defer_output_bias = False  # a block whose next norm adds the bias sets this
+        rotated_part = isinstance(position, RotaryEmbedding) and position.fused_table() is None
+        self.wide = (bias or self.value_dim != head_dim or (qk_norm_eps is not None and qk_norm_over == "projection")
+                     or head_factor is not None or gate is not None or rotated_part or self.softcap is not None
+                     or self.chunk is not None or out_bias is not None)
         self.norm_over_projection = qk_norm_eps is not None and qk_norm_over == "projection"
         self.pad_dim = head_dim
         if self.wide:
-            if position is not None:
-                raise ValueError("a position encoding on queries and keys is not built for attention with biases, a norm "
-                                 "over the whole projection or values of their own width")
+            if position is not None and (self.norm_over_projection or not isinstance(position, RotaryEmbedding)):
+                raise ValueError("with biases, a value width of its own, a head factor or a gate, queries and keys take a "
+                                 "RotaryEmbedding or no position encoding, and none together with a norm over the projection")
+            if self.norm_over_projection and (head_factor or gate):
+                raise ValueError("a head factor or an output gate is not built together with a norm over the projection")
             if qk_norm_eps is not None and qk_norm_over == "head":
                 raise ValueError("a per-head q/k norm is not built together with biases or values of their own width")
             self.pad_dim = -(-max(head_dim, self.value_dim) // 8) * 8
         sources = [(prefix + n["q"], q_heads * head_dim)]
         if not reads_only:
             sources += [(prefix + n["k"], kv_heads * head_dim), (prefix + n["v"], kv_heads * self.value_dim)]
+        if self.gate_name:
+            sources.append((self.gate_name, q_heads * self.value_dim))
         self.qkv = Linear(sources, hidden_size)
         self.out = Linear([(prefix + n["o"], hidden_size)], q_heads * self.value_dim,
                           column_groups=(q_heads, self.value_dim, self.pad_dim) if self.wide else None)
@@ -111,6 +140,10 @@ class GQAttention(Mixer):
             if not self.reads_only:
                 specs[self.bias_names[1]] = WeightSpec((self.kv_heads * self.head_dim,), "bias")
                 specs[self.bias_names[2]] = WeightSpec((self.kv_heads * self.value_dim,), "bias")
+        if self.head_factor_name:
+            specs[self.head_factor_name] = WeightSpec((self.q_heads,), "norm")
+        if self.out_bias_name:
+            specs[self.out_bias_name] = WeightSpec((self.hidden_size,), "bias")
         if self.position is not None:
             specs.update(self.position.weight_specs())
         return specs
@@ -128,17 +161,29 @@ class GQAttention(Mixer):
             if not self.reads_only:
                 self.k_bias = weights.on_device(self.bias_names[1], torch.float32)
                 self.v_bias = weights.on_device(self.bias_names[2], torch.float32)
+        if self.head_factor_name:
+            self.head_factor = weights.on_device(self.head_factor_name, torch.float32)
+        if self.out_bias_name:
+            self.out_bias = weights.on_device(self.out_bias_name, torch.float32)
         if self.position is not None:
             self.position.load(weights, rt)
+
+    def deferred_bias(self) -> Optional[torch.Tensor]:
+        """The output projection's bias, for whoever adds this mixer's output into the stream, when the block said
+        that it will (``defer_output_bias``)."""
+        return self.out_bias if self.defer_output_bias else None
 
     def takes_unscaled(self, rows: int) -> bool:
         return not self.wide and self.qkv.fuses_norms(rows)
 
     def fuses_into_norm(self, rows: int) -> bool:
-        return self.out.fuses_norms(rows)
+        return self.out_bias is None and self.out.fuses_norms(rows)
 
     def forward(self, x, batch, cache, write_cache: bool = True) -> torch.Tensor:
-        return self.out.forward(self._mix(x, batch, cache, write_cache), self.out_dtype)
+        result = self.out.forward(self._mix(x, batch, cache, write_cache), self.out_dtype)
+        if self.out_bias is not None and not self.defer_output_bias:
+            self.rt.ops.add_bias_(result, self.out_bias)
+        return result
 
     def _mix_wide(self, x, batch, cache, write_cache: bool) -> torch.Tensor:
         """[T, q_heads * pad_dim]: the stacked product in 32-bit, one preparation kernel, the attention kernels."""
@@ -148,6 +193,17 @@ class GQAttention(Mixer):
             raise ValueError("an attention layer with k and v projections of its own must fill its cache")
         table = batch.block_tables[cache.group]
         qkv = self.qkv.forward(x, torch.float32)
+        if not self.norm_over_projection:
+            rot = self.position
+            q = ops.qkv_rope_write(qkv, self.q_heads, nkv, self.head_dim, self.value_dim, self.pad_dim, self.q_bias, self.k_bias,
+                                   self.v_bias, self.head_factor, rot.inv_freq if rot is not None else None,
+                                   rot.offset if rot is not None else 0, rot.rotary_dim if rot is not None else 0,
+                                   cache.kv, table, batch.request_of_token, batch.positions, self.rt.dtype)
+            mixed = ops.paged_attention(q, cache.kv, table, batch, self.window, self.scale, chunk=self.chunk, softcap=self.softcap)
+            if self.gate_name:
+                gate_at = self.q_heads * self.head_dim + nkv * (self.head_dim + self.value_dim)
+                ops.sigmoid_gate_(mixed, qkv[:, gate_at:], self.q_heads, self.value_dim, self.pad_dim)
+            return mixed
         q = ops.qkv_wide_norm_write(qkv, self.q_heads, nkv, self.head_dim, self.value_dim, self.pad_dim, self.q_bias,
                                     self.k_bias, self.v_bias, self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps or 0.0,
                                     cache.kv, table, batch.request_of_token, batch.positions, self.rt.dtype)

@@ -16,6 +16,11 @@ Where the parts on both sides offer it, a norm is not a kernel of its own: the p
 stream and writes the norm's rows without their 1 / rms factor (``forward_into_norm``), and the product after it
 applies that factor to its result (``takes_unscaled``); see ``UnscaledNorm``.  The block asks the parts and falls
 back to the separate norm kernel when either side declines, so a part without these methods still fits.
+
+A ``pre_norm`` block may carry a ``shift`` (``parts.shift.TokenShift``): what the mixer reads, norm1's rows, is first
+mixed with the row of the token before.  The shift keeps a request's last row in a state slot of its own (the
+layer call's ``shift_cache``), the norm hands it 32-bit rows, and the first norm then stays a kernel.  A mixer whose
+output projection has a bias may leave it to the norm that adds its output into the stream (``deferred_bias``).
 """
 from __future__ import annotations
 
@@ -36,19 +41,32 @@ def _offers(part, method: str, rows: int) -> bool:
 
 
 class Block(Part):
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], arrangement: str = "pre_norm"):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], arrangement: str = "pre_norm",
+                 shift: Optional[Part] = None):
+        if shift is not None and arrangement != "pre_norm":
+            raise ValueError("a token shift is built for the pre_norm arrangement only")
         if arrangement not in ARRANGEMENTS:
             raise ValueError(f"unknown block arrangement {arrangement!r}; known: {ARRANGEMENTS}")
-        if arrangement == "pre_norm" and norm2 is None:
-            raise ValueError("the pre_norm arrangement needs a second norm")
-        if ffn is None and arrangement != "out_norm":
+        if arrangement == "pre_norm" and (ffn is None) != (norm2 is None):
+            raise ValueError("the pre_norm arrangement has a second norm exactly when it has a feed-forward")
+        if ffn is None and arrangement == "parallel":
             raise ValueError(f"the {arrangement} arrangement needs a feed-forward")
         if arrangement == "out_norm" and (ffn is None) != (norm2 is None):
             raise ValueError("the out_norm arrangement has a second norm exactly when it has a feed-forward")
         self.norm1, self.mixer, self.norm2, self.ffn, self.arrangement = norm1, mixer, norm2, ffn, arrangement
+        self.shift = shift
+        # a bias on the mixer's output is added by the second norm's kernel where both sides can
+        self._bias_to_norm2 = bool(arrangement == "pre_norm" and ffn is not None and getattr(norm2, "takes_delta_bias", False)
+                                   and hasattr(mixer, "deferred_bias"))
+        if self._bias_to_norm2:
+            mixer.defer_output_bias = True
 
     def _parts(self):
-        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
+        return [p for p in (self.norm1, self.shift, self.mixer, self.norm2, self.ffn) if p is not None]
+
+    def shift_need(self):
+        """What the block's token shift keeps per request (None without one)."""
+        return self.shift.cache_need() if self.shift is not None else None
 
     @property
     def reads_stream(self) -> bool:
@@ -78,7 +96,7 @@ class Block(Part):
     def entry_spec(self, rows: int) -> Optional[FusedNormSpec]:
         """What the block before needs to take over this block's first norm for a batch of ``rows`` tokens;
         None if the norm stays a kernel."""
-        if self.arrangement != "pre_norm" or not _offers(self.mixer, "takes_unscaled", rows):
+        if self.arrangement != "pre_norm" or self.shift is not None or not _offers(self.mixer, "takes_unscaled", rows):
             return None
         return self._spec(self.norm1)
 
@@ -88,7 +106,7 @@ class Block(Part):
         return fn() if fn is not None else None
 
     def forward(self, resid: torch.Tensor, delta, batch, cache, write_cache: bool = True,
-                following: Optional["Block"] = None) -> Tuple[torch.Tensor, object]:
+                following: Optional["Block"] = None, shift_cache=None) -> Tuple[torch.Tensor, object]:
         """Takes the stream and what the block before left: its not-yet-added output, or (if this block's
         ``entry_spec`` was offered to it as ``following``) the ``UnscaledNorm`` of the first norm.  Returns the
         stream and what this block leaves, in the same two forms."""
@@ -98,10 +116,19 @@ class Block(Part):
         if self.arrangement == "out_norm":
             return self._forward_out_norm(resid, delta, batch, cache, write_cache)
         if self.arrangement == "pre_norm":
-            n1 = delta if isinstance(delta, UnscaledNorm) else self.norm1.add_forward(resid, delta)
+            if self.shift is not None:
+                if isinstance(delta, UnscaledNorm):
+                    raise ValueError("a block with a token shift cannot follow a block that folded its first norm into a product")
+                n1 = self.shift.forward(self.norm1.add_forward(resid, delta, wide=True), batch, shift_cache)
+            else:
+                n1 = delta if isinstance(delta, UnscaledNorm) else self.norm1.add_forward(resid, delta)
+            if self.ffn is None:
+                return resid, self.mixer.forward(n1, batch, cache, write_cache)  # the next norm adds it
             spec2 = self._spec(self.norm2) if _offers(self.mixer, "fuses_into_norm", rows) and _offers(self.ffn, "takes_unscaled", rows) else None
             if spec2 is not None:
                 n2 = self.mixer.forward_into_norm(n1, batch, cache, write_cache, resid, spec2)
+            elif self._bias_to_norm2:
+                n2 = self.norm2.add_forward(resid, self.mixer.forward(n1, batch, cache, write_cache), delta_bias=self.mixer.deferred_bias())
             else:
                 n2 = self.norm2.add_forward(resid, self.mixer.forward(n1, batch, cache, write_cache))
             spec_next = following.entry_spec(rows) if following is not None and _offers(self.ffn, "fuses_into_norm", rows) else None

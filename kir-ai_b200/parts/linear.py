@@ -60,6 +60,15 @@ class Linear(Part):
         # the tensor-core product streams weights fastest from its own box layout (``ops.TiledWeight``)
         self.weight = rt.ops.tile_weight(stacked) if self.on_tensor_cores() else stacked
 
+    def load_matrix(self, matrix: torch.Tensor, rt: Runtime) -> None:
+        """Takes a ready matrix [out_features, in_features] (one that a part worked out from stored tensors) in place
+        of stored ones."""
+        self.rt = rt
+        if tuple(matrix.shape) != (self.out_features, self.in_features):
+            raise ValueError(f"matrix {tuple(matrix.shape)} does not fit a layer of {self.out_features} x {self.in_features}")
+        matrix = matrix.to(device=rt.device, dtype=rt.dtype).contiguous()
+        self.weight = rt.ops.tile_weight(matrix) if self.on_tensor_cores() else matrix
+
     def forward(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         if isinstance(x, UnscaledNorm):
             return self.rt.ops.linear_tcgen05(x.rows, self.weight, out_dtype, row_scale=x.row_scale())

@@ -1,4 +1,4 @@
-"""RMSNorm with the residual add fused in.
+"""RMSNorm and layer norm with the residual add fused in.
 
 y = x * 1/sqrt(mean(x^2) + eps) * w, statistics in 32-bit, the scale 0 when
 mean + eps is 0 (crates/llm-backend/src/core/math.rs:73-113 of the reference; the
@@ -53,3 +53,38 @@ class RMSNorm(Norm):
         """The norm of ``resid[rows] + delta[rows]`` only; the stream is left untouched."""
         out, _ = self.rt.ops.add_rmsnorm(resid, delta, self.weight, self.eps, self.rt.dtype, row_index=rows)
         return out
+
+
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias: y = (x - mean) / sqrt(var + eps) * w, var the mean of the squared
+    deviations from the mean, statistics in 32-bit.  ``add_forward`` may also take a bias [width] of the sub-layer
+    whose output it adds (``takes_delta_bias``), and can leave its rows in 32-bit for a step that goes on in 32-bit
+    (``wide``: a token shift).  It is a kernel of its own: no product takes it over."""
+
+    capture_safe = True
+    kernels_only = True
+    takes_delta_bias = True
+
+    def __init__(self, weight_name: str, width: int, eps: float):
+        self.weight_name = weight_name
+        self.width = width
+        self.eps = float(eps)
+        self.weight: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.width,), "norm")}
+
+    def load(self, weights, rt: Runtime) -> None:
+        self.rt = rt
+        self.weight = weights.on_device(self.weight_name, torch.float32)
+
+    def add_forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor] = None,
+                    wide: bool = False) -> torch.Tensor:
+        return self.rt.ops.add_layernorm(resid, delta, self.weight, self.eps, self.rt.dtype, delta_bias=delta_bias, wide=wide)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.rt.ops.add_layernorm(x, None, self.weight, self.eps, self.rt.dtype)
+
+    def add_forward_rows(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+        """The norm of ``resid[rows] + delta[rows]`` only; the stream is left untouched."""
+        return self.rt.ops.add_layernorm(resid, delta, self.weight, self.eps, self.rt.dtype, row_index=rows)

@@ -4,6 +4,12 @@ For i < rotary_dim/2: f_i = theta^(-2i/rotary_dim), angle = position * f_i (both
 32-bit), and the pair (x_i, x_{i + rotary_dim/2}) is rotated by the angle
 (crates/llm-backend/src/core/math.rs:515-529 of the reference).  The frequency
 table is made once on the host in 32-bit and kept on the device.
+
+Two options.  ``scaling`` stretches the long wavelengths, the way Llama 3.1 does: with wavelength l = 2 pi / f, a
+frequency stays where l < original / high, becomes f / factor where l > original / low, and between the two is
+(1 - s) f / factor + s f with s = (original / l - low) / (high - low).  ``offset`` rotates columns [offset, offset +
+rotary_dim) of a head instead of its first ones.  With either option the table is worked out in 64-bit and rounded
+once.
 """
 from __future__ import annotations
 
@@ -18,28 +24,55 @@ class RotaryEmbedding(PositionEncoding):
     capture_safe = True
     kernels_only = True
 
-    def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None, *, offset: int = 0,
+                 scaling: Optional[dict] = None, precise: bool = False):
         self.head_dim = head_dim
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
-        if self.rotary_dim % 2 or not 0 < self.rotary_dim <= head_dim:
-            raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {head_dim}")
+        if self.rotary_dim % 2 or not 0 < self.rotary_dim or offset < 0 or offset + self.rotary_dim > head_dim:
+            raise ValueError(f"rotary_dim {self.rotary_dim} (from column {offset}) must be even and lie inside head_dim {head_dim}")
         self.theta = float(theta)
+        self.offset = offset
+        self.scaling = None
+        if scaling is not None:
+            self.scaling = {key: float(scaling[key]) for key in ("factor", "low", "high", "original")}
+            if self.scaling["high"] == self.scaling["low"] or self.scaling["factor"] <= 0.0:
+                raise ValueError(f"frequency scaling needs high != low and a positive factor, got {scaling}")
+        self.precise = precise or scaling is not None or offset != 0
         self.inv_freq: Optional[torch.Tensor] = None
 
     def frequencies(self) -> torch.Tensor:
+        if self.precise:
+            return self._frequencies_64()
         half = self.rotary_dim // 2
         exponent = -(2.0 * torch.arange(half, dtype=torch.float32)) / float(self.rotary_dim)
         return torch.pow(torch.tensor(self.theta, dtype=torch.float32), exponent)
+
+    def _frequencies_64(self) -> torch.Tensor:
+        import math
+
+        half = self.rotary_dim // 2
+        index = torch.arange(half, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * index / float(self.rotary_dim))
+        if self.scaling is not None:
+            sc = self.scaling
+            wavelength = 2.0 * math.pi / freq
+            smooth = (sc["original"] / wavelength - sc["low"]) / (sc["high"] - sc["low"])
+            between = (1.0 - smooth) * freq / sc["factor"] + smooth * freq
+            freq = torch.where(wavelength < sc["original"] / sc["high"], freq,
+                               torch.where(wavelength > sc["original"] / sc["low"], freq / sc["factor"], between))
+        return freq.to(torch.float32)
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
         self.inv_freq = self.frequencies().to(rt.device)
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        if self.offset:
+            raise ValueError("a rotation that does not start at a head's first column runs inside the attention preparation only")
         self.rt.ops.rope_(q, positions, self.inv_freq, self.rotary_dim)
         self.rt.ops.rope_(k, positions, self.inv_freq, self.rotary_dim)
 
     def fused_table(self) -> Optional[torch.Tensor]:
         """The frequency table when the whole head is rotated (what the fused
         norm + rotation + cache-write kernel takes), else None."""
-        return self.inv_freq if self.rotary_dim == self.head_dim else None
+        return self.inv_freq if self.rotary_dim == self.head_dim and self.offset == 0 else None

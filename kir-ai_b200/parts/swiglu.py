@@ -1,4 +1,5 @@
-"""Dense SwiGLU feed-forward: down(silu(gate x) * (up x)), silu(x) = x / (1 + e^-x).
+"""Dense gated feed-forward: down(act(gate x) * (up x)); act is silu(x) = x / (1 + e^-x) (SwiGLU) or, as
+``GatedMLP(activation="gelu_tanh")``, 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))).
 
 crates/llm-backend/src/core/qwen/ops/moe.rs:31-88 and
 crates/llm-backend/src/core/math.rs:196-225 of the reference.  No biases.
@@ -17,6 +18,8 @@ class SwiGLU(FeedForward):
     capture_safe = True
     kernels_only = True
 
+    activation = "silu"
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, names: Optional[Dict[str, str]] = None):
         n = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
         n.update(names or {})
@@ -33,7 +36,7 @@ class SwiGLU(FeedForward):
         # On the tensor cores gate and up are one product whose epilogue applies silu(gate) * up:
         # their rows are interleaved in eights at load, so that a thread's 16 outputs pair up.
         self.fused_weight = None
-        if rt.dtype == torch.bfloat16 and self.intermediate_size % 8 == 0 and self.hidden_size % 8 == 0:
+        if self.activation == "silu" and rt.dtype == torch.bfloat16 and self.intermediate_size % 8 == 0 and self.hidden_size % 8 == 0:
             (gate_name, _), (up_name, _) = self.gate_up.sources
             gate = weights.stored(gate_name).to(device=rt.device, dtype=rt.dtype)
             up = weights.stored(up_name).to(device=rt.device, dtype=rt.dtype)
@@ -62,4 +65,17 @@ class SwiGLU(FeedForward):
             return ops.linear_tcgen05(x, self.fused_weight, swiglu=True)
         if self.fused_weight is not None:
             raise ValueError("SwiGLU input is not laid out for the tensor-core kernel (rows must be 16-byte aligned)")
+        if self.activation != "silu":
+            return ops.gated_activation(self.gate_up.forward(x), self.activation)
         return ops.swiglu(self.gate_up.forward(x))
+
+
+class GatedMLP(SwiGLU):
+    """The same feed-forward with the activation as an argument (``silu`` or ``gelu_tanh``)."""
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: Optional[Dict[str, str]] = None):
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"unknown activation {activation!r}; known: silu, gelu_tanh")
+        super().__init__(prefix, hidden_size, intermediate_size, names)
+        self.activation = activation

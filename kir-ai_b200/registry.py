@@ -68,6 +68,10 @@ def _register_builtin() -> None:
     from .models.zoferax import build_zoferax_plan
 
     register_architecture(ZoferaxConfig.architecture, ZoferaxConfig, build_zoferax_plan, replace=True)
+    from .config.silupel import SilupelConfig
+    from .models.silupel import build_silupel_plan
+
+    register_architecture(SilupelConfig.architecture, SilupelConfig, build_silupel_plan, replace=True)
 
 
 _register_builtin()
