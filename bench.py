@@ -256,9 +256,30 @@ DESIGN_SIZES = {
 }
 
 
+SILUPEL_LATENT = dict(heads=16, dim=64, rot_dim=64, vdim=64, kv_rank=192)  # a cached row of 256 columns a token
+SILUPEL_CHUNK = 1024
+
+
+def silupel_config(size: dict, layers: int, intermediate: int) -> dict:
+    """A Silupel config.json of one size: layers in the order recurrence, attention, latent attention, attention (and
+    so on), each with a dense gelu feed-forward as large as the dense model's; attention with the size's heads, half of
+    each head rotated (long wavelengths stretched), a soft cap and chunks of 1,024 tokens; the recurrence as wide as
+    the model."""
+    width = size["width"]
+    attention = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["vdim"],
+                 "scale": size["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": SILUPEL_CHUNK},
+                 "rot": {"base": 500000.0, "dims": size["dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    lat = dict(SILUPEL_LATENT, q_rank=width // 4 + width // 8, scale=(SILUPEL_LATENT["dim"] + SILUPEL_LATENT["rot_dim"]) ** -0.5,
+               rot={"base": 10000.0, "dims": SILUPEL_LATENT["rot_dim"]})
+    kinds = [("mingru", {"width": width}), ("attention", attention), ("latent_attention", lat), ("attention", attention)]
+    mlp = {"kind": "dense", "ff": intermediate}
+    return {"architecture": "Silupel", "width": width, "vocab": size["vocab"], "norm": {"eps": 1e-6},
+            "layers": [{"type": kinds[i % 4][0], "mixer": dict(kinds[i % 4][1]), "mlp": dict(mlp)} for i in range(layers)]}
+
+
 def design_configs(size: dict, layers: int):
-    """(Zoferax config.json, Qwen3 config.json) of one size: the same width, heads and layer count; the dense
-    feed-forward is as large as the experts that one token uses (3 I H = 2 top ff H)."""
+    """(Zoferax config.json, Qwen3 config.json, Silupel config.json) of one size: the same width, heads and layer count;
+    the dense feed-forward is as large as the experts that one token uses (3 I H = 2 top ff H)."""
     mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["vdim"], "scale": size["dim"] ** -0.5}
     mlp = {"kind": "moe", "expert": {"ff": size["ff"]}, "router": {"experts": size["experts"], "top": size["top"]}}
     zoferax = {"architecture": "Zoferax", "width": size["width"], "vocab": size["vocab"], "embedding": {"scale": size["width"] ** 0.5},
@@ -268,17 +289,19 @@ def design_configs(size: dict, layers: int):
                  num_hidden_layers=layers, num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"],
                  head_dim=size["dim"], vocab_size=size["vocab"], max_position_embeddings=40960, rms_norm_eps=1e-6,
                  rope_theta=1000000.0, tie_word_embeddings=False)
-    return zoferax, dense
+    return {"zoferax": zoferax, "qwen3-dense": dense, "silupel": silupel_config(size, layers, intermediate)}
 
 
-def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: float, size: dict, design: str, peaks) -> list:
+def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: float, size: dict, design: str, peaks,
+                 visible=None) -> list:
     """One row per entry point of a step: time, the work the DESIGN asks for (not what the kernel chose to compute), and
     that work over the time as a fraction of the measured peak (bytes over the copy bandwidth or flops over the bf16
     rate, whichever is the greater)."""
     import re
 
     width, heads, kvh, dk = size["width"], size["heads"], size["kv_heads"], size["dim"]
-    dv = size["vdim"] if design == "zoferax" else dk
+    dv = size["vdim"] if design in ("zoferax", "silupel") else dk
+    visible = visible or (lambda mask: (context_pairs, cache_rows))
     routed = size["experts"] * size["ff"]
     rows = []
     for name, (count, ms) in sorted(summary.items(), key=lambda item: -item[1][1]):
@@ -301,6 +324,13 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
                 bytes_ = 2.0 * m * k * (share if k == routed else 1) + 2.0 * n * k * min(1.0, share * max(1, m)) + m * n * 2.0 * (share if n == routed else 2)
                 label += " (experts; work = the chosen experts')"
             flops, bytes_ = flops * count, bytes_ * count
+        elif "attention" in name and "heads=" in name:
+            # a launch that says its shape: pairs and cache rows of the keys that its mask lets a query see
+            a_heads, a_kv, a_d, a_mask = (int(v) for v in re.search(r"heads=(\d+) kv=(\d+) d=(\d+) mask=(-?\d+)", name).groups())
+            pairs, rows_read = visible(a_mask)
+            shared = 1.0 if (design == "silupel" and a_kv == 1) else 2.0  # a latent row is key and value in one
+            flops = 2.0 * a_heads * 2 * a_d * pairs * count
+            bytes_ = (2.0 * a_kv * shared * a_d * rows_read + 2.0 * tokens * a_heads * 2 * a_d) * count
         elif "attention" in name:
             flops = 2.0 * heads * (dk + dv) * context_pairs * count
             bytes_ = (2.0 * kvh * (dk + dv) * cache_rows + 2.0 * tokens * heads * (dk + dv)) * count
@@ -309,6 +339,18 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
             bytes_ = tokens * (4.0 * cols + 2.0 * cols) * count
         elif "qk_norm_rope" in name:
             bytes_ = tokens * 2.0 * (2 * (heads + kvh) * dk + 2 * kvh * dk) * count
+        elif "add_layernorm" in name:
+            bytes_ = tokens * width * 14.0 * count
+        elif "token_shift" in name:
+            bytes_ = tokens * width * 6.0 * count
+        elif "mingru" in name:
+            bytes_ = tokens * width * 14.0 * count
+        elif "qkv_rope_write" in name or "latent_prepare" in name:
+            bytes_ = tokens * 6.0 * (heads * dk + kvh * (dk + dv)) * count
+        elif "sigmoid_gate" in name:
+            bytes_ = tokens * heads * dv * 8.0 * count
+        elif "gated_activation" in name:
+            bytes_ = tokens * size.get("intermediate", width) * 6.0 * count
         elif "norm_add" in name:
             bytes_ = tokens * width * 14.0 * count
         elif "add_rmsnorm" in name:
@@ -349,7 +391,10 @@ def compare_designs(args) -> int:
     out = {}
     for size_name in [s for s in args.sizes.split(",") if s]:
         size = DESIGN_SIZES[size_name]
-        for design, raw in zip(("zoferax", "qwen3-dense"), design_configs(size, layers)):
+        size = dict(size, intermediate=-(-(2 * size["top"] * size["ff"]) // (3 * 128)) * 128)
+        configs = design_configs(size, layers)
+        for design in [d for d in args.designs.split(",") if d]:
+            raw = configs[design]
             vocab = size["vocab"]
             engine = Engine(config=config_from_dict(raw), random_weights_seed=3, dtype="bfloat16", page_size=args.page_size,
                             max_new_tokens=4 * (warmup + steps) + 64, max_prefill_tokens=T, max_concurrent_requests=R,
@@ -377,7 +422,17 @@ def compare_designs(args) -> int:
             pages = runner.cache.open(("prefill", "timed"))
             with ops.launch_timer() as timer:
                 runner.step([StepEntry(pages, prompt(T), [T - 1])], check_errors=False)
-            prefill_kernels = _kernel_rows(timer.summary(), T, T * (T + 1) / 2.0, T, size, design.split("-")[0], peaks)
+            def prefill_visible(mask):
+                # pairs of (query, key it sees) and key rows read, for a prompt of T tokens from position 0
+                if mask < 0:
+                    return float(sum(p % -mask + 1 for p in range(T))), float(T)
+                return T * (T + 1) / 2.0, float(T)
+
+            def decode_visible(mask):
+                seen = (context + 1) % -mask + 1 if mask < 0 else context + 2.0
+                return R * float(seen), R * float(seen)
+
+            prefill_kernels = _kernel_rows(timer.summary(), T, T * (T + 1) / 2.0, T, size, design.split("-")[0], peaks, prefill_visible)
             runner.cache.close(pages)
             # decode: R requests at the context length; through Engine.step (captured steps, host tokens in and out)
             params = SamplingParams(temperature=0.0, max_new_tokens=4 * (warmup + steps) + 64, ignore_eos=True)
@@ -402,7 +457,8 @@ def compare_designs(args) -> int:
             runner.step([StepEntry(request, prompt(1), [0]) for request in held], check_errors=False)
             with ops.launch_timer() as timer:
                 runner.step([StepEntry(request, prompt(1), [0]) for request in held], check_errors=False)
-            decode_kernels = _kernel_rows(timer.summary(), R, R * (context + 2.0), R * (context + 2.0), size, design.split("-")[0], peaks)
+            decode_kernels = _kernel_rows(timer.summary(), R, R * (context + 2.0), R * (context + 2.0), size, design.split("-")[0], peaks,
+                                          decode_visible)
             ops.check_device_errors(runner.rt.device)
             out[f"{size_name}/{design}"] = {
                 "prefill_tokens_per_s": T / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
@@ -412,7 +468,7 @@ def compare_designs(args) -> int:
             }
             del engine, runner, held, requests
             torch.cuda.empty_cache()
-    line = {"metric": "prefill and decode tokens/s, Zoferax beside dense Qwen3 at equal layer sizes", "unit": "tokens/s", "n_gpus": 1,
+    line = {"metric": f"prefill and decode tokens/s of {args.designs} at equal layer sizes", "unit": "tokens/s", "n_gpus": 1,
             "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic: uniform-random token ids, random weights (seed 3)",
             "config": {"sizes": {k: DESIGN_SIZES[k] for k in args.sizes.split(",") if k}, "layers": layers, "prefill_tokens": T,
                        "decode_batch": R, "context": context, "page_size": args.page_size, "peaks": peak_source,
@@ -446,6 +502,8 @@ def main() -> int:
                              "Zoferax decoder beside the dense Qwen3 decoder at equal layer sizes (--sizes), with every "
                              "step's time by kernel; a line of its own.")
     parser.add_argument("--sizes", default="2k,4k", help="layer sizes of --workload designs: " + ", ".join(DESIGN_SIZES))
+    parser.add_argument("--designs", default="zoferax,qwen3-dense",
+                        help="which designs --workload designs measures, comma separated: zoferax, silupel, qwen3-dense")
     args = parser.parse_args()
 
     if args.impl == "reference":

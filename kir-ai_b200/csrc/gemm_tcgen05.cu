@@ -111,6 +111,8 @@ struct Epilogue {
     // of A's tile m are multiplied with matrix tile_group[m] (rows of A sorted by group, every group's rows padded to
     // whole tiles); a tile with a negative group holds no rows and is left out.  Null: one matrix.
     const int* tile_group = nullptr;
+    // The activation of the gated epilogue (EPI 1): 0 silu, 1 the tanh form of gelu.
+    int gate_act = 0;
 };
 
 // Clock stamps of one CTA of the streaming kernel, written only when a buffer is given: 0 the CTA starts, 1 the kernel
@@ -175,6 +177,12 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t address, float value) {
 // rounded reciprocal, a sequence with a branch for special cases, made sixteen of these take 1.9 us a thread.)
 __device__ __forceinline__ float silu_mul(float gate, float up) {
     return __fdividef(gate * up, 1.0f + __expf(-gate));
+}
+// act(gate) * up.  The tanh form of gelu, 0.5 z (1 + tanh(y)) with y = sqrt(2 / pi) (z + 0.044715 z^3), is
+// z * sigmoid(2 y): the same one exponential and one division as silu, with another argument.
+__device__ __forceinline__ float gate_mul(int act, float gate, float up) {
+    const float t = act == 1 ? 1.5957691216057308f * fmaf(0.044715f * gate * gate, gate, gate) : gate;
+    return __fdividef(gate * up, 1.0f + __expf(-t));
 }
 
 // SWAP false: X = A (rows m), Y = W (rows n), C[m, n].  SWAP true: X = W, Y = A.
@@ -465,7 +473,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float out = silu_mul(v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
+                        const float out = gate_mul(ep.gate_act, v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
                         if ((lane & 8) == 0) stage[(c0 - h0 + j) * 132 + (tile_row >> 4) * 8 + (tile_row & 7)] = out;
                     }
                 } else {
@@ -497,7 +505,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
                 float out[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) out[j] = silu_mul(v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
+                for (int j = 0; j < 16; ++j) out[j] = gate_mul(ep.gate_act, v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
                 if ((lane & 8) == 0 && x_row < x_rows) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -515,14 +523,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     uint32_t packed[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        __nv_bfloat162 pair = __floats2bfloat162_rn(silu_mul(v[2 * j], v[2 * j + 8]), silu_mul(v[2 * j + 1], v[2 * j + 9]));
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(gate_mul(ep.gate_act, v[2 * j], v[2 * j + 8]), gate_mul(ep.gate_act, v[2 * j + 1], v[2 * j + 9]));
                         packed[j] = *reinterpret_cast<uint32_t*>(&pair);
                     }
                     *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        if (y0 + c0 + j + 8 < y_rows) dst[j] = from_f32<OutT>(silu_mul(v[j], v[j + 8]));
+                        if (y0 + c0 + j + 8 < y_rows) dst[j] = from_f32<OutT>(gate_mul(ep.gate_act, v[j], v[j + 8]));
                 }
             } else if (SWAP) {
 #pragma unroll
@@ -984,14 +992,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                         uint32_t packed[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            __nv_bfloat162 pair = __floats2bfloat162_rn(silu_mul(v[2 * j], v[2 * j + 8]), silu_mul(v[2 * j + 1], v[2 * j + 9]));
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(gate_mul(ep.gate_act, v[2 * j], v[2 * j + 8]), gate_mul(ep.gate_act, v[2 * j + 1], v[2 * j + 9]));
                             packed[j] = *reinterpret_cast<uint32_t*>(&pair);
                         }
                         *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            if (y0 + c0 + j + 8 < N) dst[j] = from_f32<OutT>(silu_mul(v[j], v[j + 8]));
+                            if (y0 + c0 + j + 8 < N) dst[j] = from_f32<OutT>(gate_mul(ep.gate_act, v[j], v[j + 8]));
                     }
                 } else {
                     OutT* dst = C + (size_t)x_row * ldc + y0 + c0;
@@ -1257,7 +1265,7 @@ KIRAI_EXPORT int kirai_gemm_bf16_grouped(const void* A, const void* W, int tiled
 // The one entry point of the tensor-core product, A[M, K] (row stride lda) times W[N, K] transposed.
 //   tiled:  W is in the tiled form described at the top of this file, else row-major.
 //   form 0: C[M, N] bf16.  1: C[M, N] float.  2: C[M, N / 2] = silu(gate) * up, W's rows in groups of 8 gate rows
-//           followed by their 8 up rows.  3: residual[M, N] (float, in place) += product, C[M, N] =
+//           followed by their 8 up rows.  5: as 2 with the tanh form of gelu in place of silu.  3: residual[M, N] (float, in place) += product, C[M, N] =
 //           bf16(residual * norm_weight[n]) and sumsq_out[parts][M] = each column tile's share of sum_n residual^2.
 //   row_sumsq (forms 0-2, may be null): the rows of A were left unscaled by an RMSNorm; row m of the product is
 //           multiplied by 1 / sqrt(sum_p row_sumsq[p][m] / row_count + row_eps).
@@ -1273,6 +1281,9 @@ KIRAI_EXPORT int kirai_gemm_bf16_general(const void* A, const void* W, int tiled
         case 0: return gemm_dispatch<bf16, 0>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
         case 1: return gemm_dispatch<float, 0>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
         case 2: return gemm_dispatch<bf16, 1>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+        case 5:
+            ep.gate_act = 1;
+            return gemm_dispatch<bf16, 1>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
         case 3:
             if (!residual || !norm_weight || !sumsq_out || row_sumsq) return KIRAI_ERR_BAD_SIZE;
             ep.residual = residual, ep.norm_weight = norm_weight, ep.sumsq_out = sumsq_out;

@@ -698,6 +698,13 @@ def mask_code(window: Optional[int], chunk: Optional[int] = None) -> int:
     return -int(chunk) if chunk else int(window or 0)
 
 
+def _attention_detail(q_heads: int, kv_heads: int, head_dim: int, window: Optional[int], chunk: Optional[int]) -> str:
+    """What a launch timer's record says of an attention launch beside its entry point (nothing when no timer runs)."""
+    if _timer is None:
+        return ""
+    return f" heads={q_heads} kv={kv_heads} d={head_dim} mask={mask_code(window, chunk)}"
+
+
 def _capped(name: str, softcap: Optional[float]):
     """The entry point ``name`` or its form with a soft cap on the scores, and that form's extra argument."""
     if softcap:
@@ -719,7 +726,7 @@ def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: tor
     _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table),
           _ptr(request_of_token), _ptr(positions), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride),
           _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap,
-          _ptr(error_flag(q.device)), _stream())
+          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
     return out
 
 
@@ -776,7 +783,7 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     _call(name, _ptr(q), _ptr(cache), _ptr(out),
           _ptr(block_table), _ptr(query_start), _ptr(context_len), _i(requests), _i(max_query_len), _i(q_heads), _i(kv_heads),
           _i(head_dim), _l(q_stride), _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale),
-          *cap, _ptr(error_flag(q.device)), _stream())
+          *cap, _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
     return out
 
 
@@ -889,7 +896,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
     _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
           _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap, _i(num_splits),
-          _ptr(error_flag(q.device)), _stream())
+          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
     return out
 
 
@@ -923,7 +930,7 @@ def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table:
     _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
           _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap, _i(ctas),
-          _ptr(error_flag(q.device)), _stream())
+          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
     return out
 
 
@@ -1229,7 +1236,7 @@ def _gemm(x, weight, out, n: int, k: int, width: int, splits: int, form: int, ro
         sumsq = row_scale[0]
         assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == x.shape[0] and sumsq.is_contiguous()
     item = (x, weight, out, n, k, width, splits, form, row_scale, resid, norm_weight, sumsq_out)
-    if chaining() and isinstance(weight, TiledWeight) and x.shape[0] <= 64 and splits == 0:
+    if chaining() and isinstance(weight, TiledWeight) and x.shape[0] <= 64 and splits == 0 and form != 5:
         if _pending and _pending[0][0].shape[0] != x.shape[0]:
             flush_products()
         _pending.append(item)
@@ -1254,13 +1261,15 @@ def _check_product(x, weight) -> tuple:
 
 
 def linear_tcgen05(x: torch.Tensor, weight, out_dtype: Optional[torch.dtype] = None,
-                   splits: int = 0, swiglu: bool = False, row_scale: Optional[tuple] = None) -> torch.Tensor:
+                   splits: int = 0, swiglu: bool = False, row_scale: Optional[tuple] = None,
+                   gate_act: str = "silu") -> torch.Tensor:
     """bf16 ``x`` [M, K] times ``weight`` [N, K] transposed on the tcgen05 tensor cores (32-bit accumulation).
 
     ``weight`` is a row-major tensor or a ``TiledWeight``.  K and the row stride of ``x`` must be multiples of 8
     (TMA reads rows in 16-byte units).  ``splits`` > 1 cuts K between the CTAs of a cluster (0: chosen from the
     shape, at most 4).  With ``swiglu`` the rows of ``weight`` are 8 gate rows, their 8 up rows, 8 gate rows, ...
-    and the result is silu(gate) * up, [M, N / 2].  ``row_scale`` = (sumsq [P, M] float32, count, eps) multiplies
+    and the result is silu(gate) * up, [M, N / 2] (``gate_act`` "gelu_tanh": the tanh form of gelu in place of silu).
+    ``row_scale`` = (sumsq [P, M] float32, count, eps) multiplies
     row m of the product by 1 / sqrt(sum_p sumsq[p, m] / count + eps): ``x`` then holds rows that an RMSNorm left
     unscaled.
     """
@@ -1270,7 +1279,8 @@ def linear_tcgen05(x: torch.Tensor, weight, out_dtype: Optional[torch.dtype] = N
         assert out_dtype == torch.bfloat16 and n % 16 == 0
     width = n // 2 if swiglu else n
     out = torch.empty((m, width), dtype=out_dtype, device=x.device)
-    form = 2 if swiglu else (0 if out_dtype == torch.bfloat16 else 1)
+    form = (5 if gate_act == "gelu_tanh" else 2) if swiglu else (0 if out_dtype == torch.bfloat16 else 1)
+    assert gate_act in GATED_ACTIVATIONS
     _gemm(x, weight, out, n, k, width, splits, form, row_scale, None, None, None)
     return out
 

@@ -32,7 +32,8 @@ def _rotary(head_dim: int, rot) -> RotaryEmbedding:
     return RotaryEmbedding(head_dim, rot.base, rot.dims, scaling=scaling, precise=True)
 
 
-def _mixer(cfg: SilupelConfig, layer, prefix: str):
+def mixer_for_layer(cfg: SilupelConfig, layer, prefix: str):
+    """The mixer of one configured layer, its tensors under ``prefix``."""
     m = layer.mixer
     if layer.kind == "mingru":
         return MinGRU(prefix, cfg.width, m.width)
@@ -52,7 +53,7 @@ def build_silupel_plan(cfg: SilupelConfig) -> ModelPlan:
         if layer.mlp is not None:
             ffn = GatedMLP(base + "mlp.", cfg.width, layer.mlp.ff, "gelu_tanh", names=_MLP_NAMES)
             norm2 = LayerNorm(base + "norm2", cfg.width, cfg.norm_eps)
-        blocks.append(Block(LayerNorm(base + "norm1", cfg.width, cfg.norm_eps), _mixer(cfg, layer, base + "mix."), norm2, ffn,
+        blocks.append(Block(LayerNorm(base + "norm1", cfg.width, cfg.norm_eps), mixer_for_layer(cfg, layer, base + "mix."), norm2, ffn,
                             arrangement="pre_norm", shift=TokenShift(base + "shift", cfg.width)))
     # every run of a layer has a cache layer for its mixer and one for its token shift
     order, next_cache = [], 0

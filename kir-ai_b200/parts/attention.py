@@ -85,9 +85,9 @@ class GQAttention(Mixer):
         self.out_bias_name = prefix + out_bias if out_bias else None
         self.head_factor = self.out_bias = None
         self.defer_output_bias = False  # a block whose next norm adds the bias sets this
-        rotated_part = isinstance(position, RotaryEmbedding) and position.fused_table() is None
+        shifted_rotation = isinstance(position, RotaryEmbedding) and position.offset != 0
         self.wide = (bias or self.value_dim != head_dim or (qk_norm_eps is not None and qk_norm_over == "projection")
-                     or head_factor is not None or gate is not None or rotated_part or self.softcap is not None
+                     or head_factor is not None or gate is not None or shifted_rotation or self.softcap is not None
                      or self.chunk is not None or out_bias is not None)
         self.norm_over_projection = qk_norm_eps is not None and qk_norm_over == "projection"
         self.pad_dim = head_dim

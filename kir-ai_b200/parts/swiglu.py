@@ -33,10 +33,10 @@ class SwiGLU(FeedForward):
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
         self.down.load(weights, rt)
-        # On the tensor cores gate and up are one product whose epilogue applies silu(gate) * up:
+        # On the tensor cores gate and up are one product whose epilogue applies act(gate) * up:
         # their rows are interleaved in eights at load, so that a thread's 16 outputs pair up.
         self.fused_weight = None
-        if self.activation == "silu" and rt.dtype == torch.bfloat16 and self.intermediate_size % 8 == 0 and self.hidden_size % 8 == 0:
+        if rt.dtype == torch.bfloat16 and self.intermediate_size % 8 == 0 and self.hidden_size % 8 == 0:
             (gate_name, _), (up_name, _) = self.gate_up.sources
             gate = weights.stored(gate_name).to(device=rt.device, dtype=rt.dtype)
             up = weights.stored(up_name).to(device=rt.device, dtype=rt.dtype)
@@ -60,9 +60,9 @@ class SwiGLU(FeedForward):
         """silu(gate x) * (up x): [T, I]."""
         ops = self.rt.ops
         if isinstance(x, UnscaledNorm):
-            return ops.linear_tcgen05(x.rows, self.fused_weight, swiglu=True, row_scale=x.row_scale())
+            return ops.linear_tcgen05(x.rows, self.fused_weight, swiglu=True, row_scale=x.row_scale(), gate_act=self.activation)
         if self.fused_weight is not None and ops.tcgen05_takes(x):
-            return ops.linear_tcgen05(x, self.fused_weight, swiglu=True)
+            return ops.linear_tcgen05(x, self.fused_weight, swiglu=True, gate_act=self.activation)
         if self.fused_weight is not None:
             raise ValueError("SwiGLU input is not laid out for the tensor-core kernel (rows must be 16-byte aligned)")
         if self.activation != "silu":
