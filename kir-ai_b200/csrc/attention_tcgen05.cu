@@ -391,7 +391,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             if (form.cap_log2 != 0.0f) {
 #pragma unroll
                 for (int i = 0; i < TA_BN; ++i)
-                    s[i] = __float_as_uint(form.cap_log2 * tanh_from_exp(__uint_as_float(s[i]) * form.cap_in));
+                    s[i] = __float_as_uint(capped_exponent(__uint_as_float(s[i]), form));
             }
             // a tile whose keys every row of this warp sees needs no mask
             const bool interior = __all_sync(0xffffffffu, j0 >= lo && j0 + TA_BN - 1 <= pos);

@@ -89,29 +89,33 @@ __host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
     return 0;
 }
 
-// tanh in 32-bit from one exponential: 1 - 2 / (e^(2x) + 1); the absolute error stays near 1e-7.
-__device__ __forceinline__ float tanh_from_exp(float x) {
-    x = fminf(fmaxf(x, -15.0f), 15.0f);             // tanh is +-1 in 32-bit beyond that
-    const float e = exp2f(x * 2.885390081777927f);  // e^(2x)
-    return 1.0f - __fdividef(2.0f, e + 1.0f);
-}
-
 // A raw score (q . k) in the base-2 exponent's units: times scale * log2(e), or, with a soft cap c,
-// c * tanh(score * scale / c) * log2(e).  cap_log2 = c * log2(e) (0: no cap), cap_in = scale / c.
+// c * tanh(score * scale / c) * log2(e).  tanh(x) = 1 - 2 / (e^(2x) + 1) costs one exponential and one reciprocal (the
+// absolute error stays near 1e-7; large |x| needs no clamp: the exponential gives inf or 0 there, and the reciprocal of
+// inf is 0), and the factors around it are folded on the host: cap_in = 2 log2(e) scale / c, cap_log2 = c log2(e)
+// (0: no cap), cap_out = -2 cap_log2, so that a capped score is a multiply, ex2, an add, rcp and a multiply-add.
 struct ScoreForm {
-    float scale_log2, cap_in, cap_log2;
+    float scale_log2, cap_in, cap_log2, cap_out;
 };
 
 static inline ScoreForm make_score_form(float scale, float softcap) {
     ScoreForm form;
     form.scale_log2 = scale * 1.4426950408889634f;
-    form.cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
+    form.cap_in = softcap > 0.0f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.0f;
     form.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+    form.cap_out = -2.0f * form.cap_log2;
     return form;
 }
 
+__device__ __forceinline__ float capped_exponent(float raw, const ScoreForm& form) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(raw * form.cap_in));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(form.cap_out, r, form.cap_log2);
+}
+
 __device__ __forceinline__ float score_exponent(float raw, const ScoreForm& form) {
-    return form.cap_log2 != 0.0f ? form.cap_log2 * tanh_from_exp(raw * form.cap_in) : raw * form.scale_log2;
+    return form.cap_log2 != 0.0f ? capped_exponent(raw, form) : raw * form.scale_log2;
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }

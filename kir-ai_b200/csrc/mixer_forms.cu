@@ -21,10 +21,46 @@
 // ------------------------------------------------------------ add + layer norm
 // One block per produced row.  resid[row] += delta[row] + delta_bias (when the stream is updated: no row_index);
 // out[row] = LN(resid[row]) * weight.  With row_index only those rows are produced, the stream stays as it is.
+// With a token shift (mu, state, slots given; a step in which every request brings ONE token, row r being request
+// r's): the normed row h is mixed with the request's slot, out = h + (state[slot] - h) * mu, and the slot gets h.
+struct ShiftArgs {
+    const float* mu;
+    float* state;
+    const int* slots;
+    int num_slots;
+};
+
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+}
+template <>
+__device__ __forceinline__ void load4<bf16>(const bf16* p, float (&v)[4]) {
+    const uint2 q = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&q.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&q.y);
+    v[0] = __low2float(lo), v[1] = __high2float(lo), v[2] = __low2float(hi), v[3] = __high2float(hi);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 q;
+    q.x = *reinterpret_cast<const uint32_t*>(&lo), q.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = q;
+}
+
 template <typename T, typename O>
 __global__ void add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ delta_bias,
                                      const float* __restrict__ weight, O* __restrict__ out, const int* __restrict__ row_index,
-                                     int hidden, float eps) {
+                                     int hidden, float eps, ShiftArgs shift) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float row_s[];  // [hidden]
@@ -51,14 +87,124 @@ __global__ void add_layernorm_kernel(float* __restrict__ resid, const T* __restr
     const float variance = block_sum(dev, scratch) / (float)hidden + eps;
     const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
     O* dst = out + (size_t)produced * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<O>((row_s[i] - mean) * scale * weight[i]);
+    float* kept = nullptr;
+    if (shift.mu) {
+        const int slot = shift.slots[produced];
+        if (slot < 0 || slot >= shift.num_slots) return;
+        kept = shift.state + (size_t)slot * hidden;
+    }
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float h = (row_s[i] - mean) * scale * weight[i];
+        if (kept) {
+            const float before = kept[i];
+            kept[i] = h;
+            h += (before - h) * shift.mu[i];
+        }
+        dst[i] = from_f32<O>(h);
+    }
+}
+
+// The same with 16-byte loads and the row kept in registers (width a multiple of 4, at most 4 * VEC * blockDim values,
+// every pointer on a 16-byte boundary).
+template <typename T, typename O, int VEC>
+__global__ void add_layernorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ delta_bias,
+                                         const float* __restrict__ weight, O* __restrict__ out, const int* __restrict__ row_index,
+                                         int hidden, float eps, ShiftArgs shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int produced = blockIdx.x;
+    const size_t row = row_index ? (size_t)row_index[produced] : (size_t)produced;
+    float* x = resid + row * hidden;
+    const T* d = delta ? delta + row * hidden : nullptr;
+    const int quads = hidden >> 2;
+    float kept[VEC][4];
+    float acc = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = (threadIdx.x + n * blockDim.x) * 4;
+        if (i < hidden) {
+            load4<float>(x + i, kept[n]);
+            if (d) {
+                float add[4];
+                load4<T>(d + i, add);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) kept[n][j] += add[j];
+            }
+            if (delta_bias) {
+                float add[4];
+                load4<float>(delta_bias + i, add);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) kept[n][j] += add[j];
+            }
+            if (!row_index && (d || delta_bias)) store4<float>(x + i, kept[n]);
+            acc += (kept[n][0] + kept[n][1]) + (kept[n][2] + kept[n][3]);
+        }
+    }
+    (void)quads;
+    const float mean = block_sum(acc, scratch) / (float)hidden;
+    float dev = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = (threadIdx.x + n * blockDim.x) * 4;
+        if (i < hidden) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                kept[n][j] -= mean;
+                dev = fmaf(kept[n][j], kept[n][j], dev);
+            }
+        }
+    }
+    const float variance = block_sum(dev, scratch) / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    O* dst = out + (size_t)produced * hidden;
+    float* slot_row = nullptr;
+    if (shift.mu) {
+        const int slot = shift.slots[produced];
+        if (slot < 0 || slot >= shift.num_slots) return;
+        slot_row = shift.state + (size_t)slot * hidden;
+    }
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = (threadIdx.x + n * blockDim.x) * 4;
+        if (i < hidden) {
+            float w[4], h[4];
+            load4<float>(weight + i, w);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = kept[n][j] * scale * w[j];
+            if (slot_row) {
+                float before[4], mu[4];
+                load4<float>(slot_row + i, before);
+                load4<float>(shift.mu + i, mu);
+                store4<float>(slot_row + i, h);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] += (before[j] - h[j]) * mu[j];
+            }
+            store4<O>(dst + i, h);
+        }
+    }
 }
 
 template <typename T, typename O>
 static int add_layernorm_launch(float* resid, const void* delta, const float* delta_bias, const float* weight, void* out,
-                                const int* row_index, int rows, int hidden, float eps, cudaStream_t stream) {
+                                const int* row_index, int rows, int hidden, float eps, ShiftArgs shift, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || (size_t)hidden * sizeof(float) > 200 * 1024) return KIRAI_ERR_BAD_SIZE;
+    if (shift.mu && (!shift.state || !shift.slots || row_index)) return KIRAI_ERR_BAD_SIZE;
+    const bool aligned = hidden % 4 == 0 && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)delta_bias | (uintptr_t)weight |
+                                              (uintptr_t)out | (uintptr_t)shift.mu | (uintptr_t)shift.state) & 15) == 0;
+    if (aligned && hidden <= 4 * 4 * 512) {
+        const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+        const int vec = (hidden / 4 + threads - 1) / threads;
+#define KIRAI_LN(V)                                                                                                       \
+    if (vec <= V)                                                                                                         \
+        return launch_pdl(add_layernorm_vec_kernel<T, O, V>, dim3(rows), dim3(threads), 0, stream, 1u, resid, (const T*)delta, \
+                          delta_bias, weight, (O*)out, row_index, hidden, eps, shift)
+        KIRAI_LN(1);
+        KIRAI_LN(2);
+        KIRAI_LN(4);
+#undef KIRAI_LN
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     auto kernel = add_layernorm_kernel<T, O>;
     if (smem > 48 * 1024) {
@@ -67,20 +213,26 @@ static int add_layernorm_launch(float* resid, const void* delta, const float* de
     }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     return launch_pdl(kernel, dim3(rows), dim3(threads), smem, stream, 1u, resid, (const T*)delta, delta_bias, weight, (O*)out,
-                      row_index, hidden, eps);
+                      row_index, hidden, eps, shift);
 }
 
-// delta in the runtime dtype (f32 / bf16); the normed rows in that dtype, or (``wide``) in 32-bit for a token shift.
+// delta in the runtime dtype (f32 / bf16); the normed rows in that dtype, or (``wide``) in 32-bit for a token shift
+// that runs as a kernel of its own.  shift_mu, shift_state [num_slots, hidden], slots: the fused token shift of a
+// step of single tokens (all null: none).
 KIRAI_EXPORT int kirai_add_layernorm_f32(float* resid, const void* delta, const float* delta_bias, const float* weight,
                                          void* out, const int* row_index, int rows, int hidden, float eps, int wide,
+                                         const float* shift_mu, float* shift_state, const int* slots, int num_slots,
                                          cudaStream_t stream) {
-    return add_layernorm_launch<float, float>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, stream);
+    return add_layernorm_launch<float, float>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps,
+                                              ShiftArgs{shift_mu, shift_state, slots, num_slots}, stream);
 }
 KIRAI_EXPORT int kirai_add_layernorm_bf16(float* resid, const void* delta, const float* delta_bias, const float* weight,
                                           void* out, const int* row_index, int rows, int hidden, float eps, int wide,
+                                          const float* shift_mu, float* shift_state, const int* slots, int num_slots,
                                           cudaStream_t stream) {
-    if (wide) return add_layernorm_launch<bf16, float>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, stream);
-    return add_layernorm_launch<bf16, bf16>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, stream);
+    const ShiftArgs shift{shift_mu, shift_state, slots, num_slots};
+    if (wide) return add_layernorm_launch<bf16, float>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, shift, stream);
+    return add_layernorm_launch<bf16, bf16>(resid, delta, delta_bias, weight, out, row_index, rows, hidden, eps, shift, stream);
 }
 
 // ------------------------------------------------------------------ token shift
@@ -167,6 +319,7 @@ __global__ void mingru_walk_kernel(const float* __restrict__ zxg, long row_strid
     const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
     pdl_wait();
     float s = state[(size_t)slot * width + ch];
+#pragma unroll 4
     for (int t = first; t < end; ++t) {
         const float* row = zxg + (size_t)t * row_stride;
         float z, c;
@@ -178,7 +331,7 @@ __global__ void mingru_walk_kernel(const float* __restrict__ zxg, long row_strid
     state[(size_t)slot * width + ch] = s;
 }
 
-#define SCAN_PIECE 64
+#define SCAN_PIECE 32
 
 // Pieces of SCAN_PIECE tokens, counted from the request's first row of this step.  Pass 1: a thread per (piece,
 // channel) leaves the piece's decay (product of 1 - z) and its end state from a zero start.
@@ -194,6 +347,7 @@ __global__ void mingru_piece_kernel(const float* __restrict__ zxg, long row_stri
     const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
     pdl_wait();
     float a = 1.0f, s = 0.0f;
+#pragma unroll 4
     for (int t = first; t < end; ++t) {
         float z, c;
         mingru_terms(zxg + (size_t)t * row_stride, width, ch, zb, xb, z, c);
@@ -242,6 +396,7 @@ __global__ void mingru_rows_kernel(const float* __restrict__ zxg, long row_strid
     const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
     pdl_wait();
     float s = incoming[((size_t)request * max_pieces + piece) * width + ch];
+#pragma unroll 4
     for (int t = first; t < end; ++t) {
         const float* row = zxg + (size_t)t * row_stride;
         float z, c;

@@ -350,11 +350,21 @@ def qkv_wide_norm_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim:
 # ------------------------------------------------ layer norm, token shift, recurrences
 def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                   out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None, delta_bias: Optional[torch.Tensor] = None,
-                  wide: bool = False) -> torch.Tensor:
+                  wide: bool = False, shift: Optional[tuple] = None) -> torch.Tensor:
     """``resid += delta + delta_bias`` (32-bit, in place), then the layer norm with a weight and no bias of the sum:
     (x - mean) / sqrt(var + eps) * weight, in ``out_dtype`` (``wide``: in 32-bit whatever the runtime dtype, for a
-    step that goes on in 32-bit).  With ``row_index`` only those rows are produced and the stream is left as it is."""
+    step that goes on in 32-bit).  With ``row_index`` only those rows are produced and the stream is left as it is.
+    ``shift`` = (mu [H], state [slots, H], slots [rows]), all on the device, for a step in which every request brings
+    one token and row r is request r's: the token shift runs in the same kernel (normed row h becomes
+    h + (state[slot] - h) * mu, and the slot gets h)."""
     _need_cuda(resid, delta, weight, row_index, delta_bias)
+    mu = state = slots = None
+    if shift is not None:
+        mu, state, slots = shift
+        _need_cuda(mu, state, slots)
+        assert row_index is None and not wide and slots.dtype == torch.int32 and slots.numel() == resid.shape[0]
+        assert mu.dtype == torch.float32 and mu.numel() == resid.shape[1] and mu.is_contiguous()
+        assert state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == resid.shape[1] and state.is_contiguous()
     assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
     hidden = resid.shape[1]
     assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == hidden
@@ -367,7 +377,8 @@ def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: to
     rows = resid.shape[0] if row_index is None else row_index.numel()
     out = torch.empty((rows, hidden), dtype=torch.float32 if wide else out_dtype, device=resid.device)
     _call(f"kirai_add_layernorm_{_suffix(out_dtype)}", _ptr(resid), _ptr(delta), _ptr(delta_bias), _ptr(weight), _ptr(out),
-          _ptr(row_index), _i(rows), _i(hidden), _f(eps), _i(1 if wide else 0), _stream())
+          _ptr(row_index), _i(rows), _i(hidden), _f(eps), _i(1 if wide else 0), _ptr(mu), _ptr(state), _ptr(slots),
+          _i(state.shape[0] if state is not None else 0), _stream())
     return out
 
 

@@ -119,7 +119,11 @@ class Block(Part):
             if self.shift is not None:
                 if isinstance(delta, UnscaledNorm):
                     raise ValueError("a block with a token shift cannot follow a block that folded its first norm into a product")
-                n1 = self.shift.forward(self.norm1.add_forward(resid, delta, wide=True), batch, shift_cache)
+                if batch.max_query_len == 1 and getattr(self.norm1, "fuses_shift", False) and hasattr(self.shift, "fused_args"):
+                    # every request brings one token: the shift runs inside the norm's kernel
+                    n1 = self.norm1.add_forward(resid, delta, shift=self.shift.fused_args(batch, shift_cache))
+                else:
+                    n1 = self.shift.forward(self.norm1.add_forward(resid, delta, wide=True), batch, shift_cache)
             else:
                 n1 = delta if isinstance(delta, UnscaledNorm) else self.norm1.add_forward(resid, delta)
             if self.ffn is None:

@@ -64,6 +64,7 @@ class LayerNorm(Norm):
     capture_safe = True
     kernels_only = True
     takes_delta_bias = True
+    fuses_shift = True  # add_forward(shift=...) runs a token shift of single-token steps inside the norm's kernel
 
     def __init__(self, weight_name: str, width: int, eps: float):
         self.weight_name = weight_name
@@ -79,8 +80,9 @@ class LayerNorm(Norm):
         self.weight = weights.on_device(self.weight_name, torch.float32)
 
     def add_forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor] = None,
-                    wide: bool = False) -> torch.Tensor:
-        return self.rt.ops.add_layernorm(resid, delta, self.weight, self.eps, self.rt.dtype, delta_bias=delta_bias, wide=wide)
+                    wide: bool = False, shift: Optional[tuple] = None) -> torch.Tensor:
+        return self.rt.ops.add_layernorm(resid, delta, self.weight, self.eps, self.rt.dtype, delta_bias=delta_bias, wide=wide,
+                                         shift=shift)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.rt.ops.add_layernorm(x, None, self.weight, self.eps, self.rt.dtype)

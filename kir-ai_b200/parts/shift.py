@@ -35,3 +35,7 @@ class TokenShift(Part):
     def forward(self, rows: torch.Tensor, batch, cache) -> torch.Tensor:
         """``rows`` [T, width] (float32); ``cache`` a StateLayerView of [slots, width]."""
         return self.rt.ops.token_shift(rows, self.weight, cache.state, batch, self.rt.dtype)
+
+    def fused_args(self, batch, cache) -> tuple:
+        """What a norm's kernel needs to run this shift itself in a step of single tokens: (mu, state, slots)."""
+        return (self.weight, cache.state, batch.slots)

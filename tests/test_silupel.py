@@ -246,6 +246,34 @@ def test_token_shift_carries_the_last_row_between_steps_and_starts_from_zero(dty
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [64, 100, 7, 2048 + 8])
+def test_norm_and_shift_in_one_kernel_for_steps_of_single_tokens(dtype, width):
+    """Three requests, one token each a step: the norm's kernel mixes its row with the request's slot and leaves the
+    row there; over five steps that equals norm then shift over each request's five rows."""
+    from part_helpers import Session, load_part
+    from kirai_b200.parts import LayerNorm, TokenShift
+
+    norm, shift = LayerNorm("n", width, 1e-5), TokenShift("mu", width)
+    w = load_part(norm, dtype, seed=1)["n"].double()
+    mu = load_part(shift, dtype, seed=2)["mu"].double() * 6
+    shift.weight = mu.float().cuda()
+    session = Session([shift.cache_need()], dtype, num_slots=4)
+    g = torch.Generator().manual_seed(width)
+    streams = {name: torch.randn((5, width), generator=g) * 2 for name in "pqr"}
+    deltas = {name: torch.randn((5, width), generator=g).to(dtype) for name in "pqr"}
+    expected = {name: plain.token_shift(plain.layer_norm(streams[name].double() + deltas[name].double(), w, 1e-5), mu) for name in "pqr"}
+    for t in range(5):
+        batch = session.batch([(name, 1) for name in "pqr"])
+        resid = torch.stack([streams[name][t] for name in "pqr"]).cuda()
+        delta = torch.stack([deltas[name][t] for name in "pqr"]).cuda()
+        got = norm.add_forward(resid, delta, shift=shift.fused_args(batch, session.cache.layer_view(0))).float().cpu()
+        for row, name in enumerate("pqr"):
+            close(dtype, got[row], expected[name][t], f"{name} at {t}")
+        session.commit()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width,hidden", [(48, 64), (36, 100), (7, 24), (200, 64)])
 def test_mingru_walked_scanned_and_carried(dtype, width, hidden):
     """The recurrence over runs of 1 to 150 tokens, cut into steps in three ways; runs above the walk limit take the
