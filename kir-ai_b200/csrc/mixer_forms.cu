@@ -239,7 +239,7 @@ KIRAI_EXPORT int kirai_add_layernorm_bf16(float* resid, const void* delta, const
 // One block per token row.  The row before a request's first row of this step is its slot of `state`; the block of
 // that first row reads the slot and then puts the request's last row of this step there, so no slot is read and
 // written by different blocks.
-template <typename O>
+template <typename O, bool VEC>
 __global__ void token_shift_kernel(const float* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state,
                                    const int* __restrict__ request_of_token, const int* __restrict__ query_start,
                                    const int* __restrict__ slots, O* __restrict__ out, int hidden, int num_slots) {
@@ -251,21 +251,33 @@ __global__ void token_shift_kernel(const float* __restrict__ h, const float* __r
     pdl_wait();
     const float* cur = h + (size_t)row * hidden;
     O* dst = out + (size_t)row * hidden;
-    if (row != first) {
-        const float* prev = cur - hidden;
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-            const float c = cur[i];
-            dst[i] = from_f32<O>(c + (prev[i] - c) * mu[i]);
+    const bool is_first = row == first;
+    if (is_first && (slot < 0 || slot >= num_slots)) return;
+    float* kept = is_first ? state + (size_t)slot * hidden : nullptr;
+    const float* prev = is_first ? kept : cur - hidden;
+    const float* end = h + (size_t)last * hidden;
+    if (VEC) {
+        // four columns at a time (the width and every pointer allow 16-byte accesses; see the launch)
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float c[4], p[4], m[4];
+            load4<float>(cur + i, c);
+            load4<float>(prev + i, p);
+            load4<float>(mu + i, m);
+            if (is_first) {
+                float e[4];
+                load4<float>(end + i, e);
+                store4<float>(kept + i, e);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) c[j] += (p[j] - c[j]) * m[j];
+            store4<O>(dst + i, c);
         }
         return;
     }
-    if (slot < 0 || slot >= num_slots) return;
-    float* kept = state + (size_t)slot * hidden;
-    const float* end = h + (size_t)last * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float c = cur[i];
-        const float p = kept[i];
-        kept[i] = end[i];
+        const float p = prev[i];
+        if (is_first) kept[i] = end[i];
         dst[i] = from_f32<O>(c + (p - c) * mu[i]);
     }
 }
@@ -276,9 +288,10 @@ static int token_shift_launch(const float* h, const float* mu, float* state, con
                               cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0) return KIRAI_ERR_BAD_SIZE;
-    const int threads = hidden >= 1024 ? 256 : 128;
-    return launch_pdl(token_shift_kernel<O>, dim3(rows), dim3(threads), 0, stream, 1u, h, mu, state, request_of_token,
-                      query_start, slots, (O*)out, hidden, num_slots);
+    const int threads = hidden >= 4096 ? 256 : 128;
+    const bool vec = hidden % 4 == 0 && (((uintptr_t)h | (uintptr_t)mu | (uintptr_t)state | (uintptr_t)out) & 15) == 0;
+    return launch_pdl(vec ? token_shift_kernel<O, true> : token_shift_kernel<O, false>, dim3(rows), dim3(threads), 0, stream, 1u, h,
+                      mu, state, request_of_token, query_start, slots, (O*)out, hidden, num_slots);
 }
 
 KIRAI_EXPORT int kirai_token_shift_f32(const float* h, const float* mu, float* state, const int* request_of_token,
@@ -331,7 +344,7 @@ __global__ void mingru_walk_kernel(const float* __restrict__ zxg, long row_strid
     state[(size_t)slot * width + ch] = s;
 }
 
-#define SCAN_PIECE 32
+#define SCAN_PIECE 16
 
 // Pieces of SCAN_PIECE tokens, counted from the request's first row of this step.  Pass 1: a thread per (piece,
 // channel) leaves the piece's decay (product of 1 - z) and its end state from a zero start.
@@ -656,12 +669,29 @@ KIRAI_EXPORT int kirai_latent_prepare_bf16(const float* down, long down_stride, 
 // ------------------------------------------------------------- element-wise steps
 // x [T, heads, dpad] (in place) *= sigmoid(gate[T, heads * used]) on the first `used` columns of every head; gate is
 // a run of columns of a 32-bit product (row stride gate_stride).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, const float* __restrict__ gate, long gate_stride, long rows, int heads,
                                     int used, int dpad) {
     pdl_launch_dependents();
     pdl_wait();
     const long per_row = (long)heads * used;
+    if (VEC) {
+        // four columns of one head at a time (used, dpad, the gate's stride and the pointers allow 16-byte accesses)
+        const long quads = rows * per_row / 4;
+        for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < quads; at += (long)gridDim.x * blockDim.x) {
+            const long row = (at * 4) / per_row;
+            const int col = (int)(at * 4 - row * per_row);
+            const int head = col / used, c = col - head * used;
+            T* p = x + (row * heads + head) * dpad + c;
+            float v[4], g[4];
+            load4<T>(p, v);
+            load4<float>(gate + row * gate_stride + col, g);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] *= sigmoid_f32(g[j]);
+            store4<T>(p, v);
+        }
+        return;
+    }
     const long total = rows * per_row;
     for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
         const long row = at / per_row;
@@ -677,11 +707,12 @@ static int sigmoid_gate_launch(void* x, const float* gate, long gate_stride, int
                                cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (heads <= 0 || used <= 0 || dpad < used) return KIRAI_ERR_BAD_SIZE;
-    const long total = (long)rows * heads * used;
+    const bool vec = used % 4 == 0 && dpad % 4 == 0 && gate_stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)gate) & 15) == 0;
+    const long total = (long)rows * heads * used / (vec ? 4 : 1);
     const int threads = 256;
     const unsigned blocks = (unsigned)min((total + threads - 1) / threads, (long)148 * 16);
-    return launch_pdl(sigmoid_gate_kernel<T>, dim3(blocks), dim3(threads), 0, stream, 1u, (T*)x, gate, gate_stride, (long)rows, heads,
-                      used, dpad);
+    return launch_pdl(vec ? sigmoid_gate_kernel<T, true> : sigmoid_gate_kernel<T, false>, dim3(blocks), dim3(threads), 0, stream, 1u,
+                      (T*)x, gate, gate_stride, (long)rows, heads, used, dpad);
 }
 
 KIRAI_EXPORT int kirai_sigmoid_gate_f32(void* x, const float* gate, long gate_stride, int rows, int heads, int used, int dpad,
