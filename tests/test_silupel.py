@@ -621,6 +621,84 @@ def test_long_prompts_whole_in_portions_and_beside_decoded_tokens(dtype, tmp_pat
     assert replay.close() == 0
 
 
+def random_configuration(seed):
+    """A configuration drawn from sizes that are and are not multiples of 8, any order and number of layers, layers
+    without feed-forward, every option present or absent, a loop over any stretch."""
+    import random
+
+    r = random.Random(seed)
+    width = r.choice([32, 40, 72, 96, 130])
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        kind = r.choice(["mingru", "attention", "latent_attention"])
+        if kind == "mingru":
+            entry = gru(r.choice([8, 20, 64, 100]))
+        elif kind == "attention":
+            kv_heads, dim = r.choice([1, 2, 3, 4]), r.choice([8, 12, 16, 24, 32, 40, 64])
+            dims = r.choice([d for d in (2, 4, 6, 8, 16, 32, 64) if d <= dim] + [dim])
+            scaling = r.choice([None, (r.choice([2.0, 8.0]), 1.0, r.choice([2.0, 4.0]), r.choice([8, 64]))])
+            entry = attn(kv_heads * r.choice([1, 2, 3, 4, 5, 8]), kv_heads, dim, r.choice([8, 12, 16, 24, 32, 40, 64]),
+                         r.uniform(0.5, 1.5) * 4 / dim ** 0.5, rot(r.choice([50.0, 10000.0, 1e6]), dims, scaling),
+                         softcap=r.choice([None, 2.5, 8.0, 30.0]), chunk=r.choice([None, 1, 3, 7, 16, 33, 64, 200]))
+        else:
+            rot_dim = r.choice([2, 4, 6, 8, 16, 32])
+            entry = latent(r.choice([1, 2, 4, 6, 8, 20]), r.choice([4, 8, 10, 16, 32]), rot_dim, r.choice([4, 8, 12, 16]),
+                           r.choice([8, 20, 24, 48]), r.choice([6, 16, 18, 32, 64]), r.uniform(0.5, 1.5),
+                           base=r.choice([100.0, 10000.0]), scaling=r.choice([None, (4.0, 1.0, 2.0, 16)]))
+        layers.append(layer(entry, r.choice([None, 16, 36, 52, 96])))
+    raw = {"architecture": "Silupel", "width": width, "vocab": r.choice([50, 97, 260]), "norm": {"eps": r.choice([1e-6, 1e-5, 1e-3])},
+           "layers": layers}
+    if r.random() < 0.6:
+        start = r.randrange(len(layers))
+        raw["loop"] = {"start": start, "stop": r.randint(start + 1, len(layers)), "times": r.randint(1, 3)}
+    return raw, r.choice([4, 8, 16, 16])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_whole_in_portions_and_mixed(seed, dtype, tmp_path):
+    """Three requests of a randomly drawn configuration: one whole, one in portions with its last tokens one by one,
+    and all three side by side in unequal runs, on four slots that are given back and used again."""
+    from kirai_b200.engine.batch import StepEntry
+    from kirai_b200.engine.runner import ModelRunner
+
+    raw, page = random_configuration(seed)
+    folder = str(tmp_path / "model")
+    write_model(folder, raw, 100 + seed)
+    config, weights = read_model_folder(folder)
+    sequences = {rid: random_tokens(n, raw["vocab"], 300 + seed + k) for k, (rid, n) in enumerate([("a", 83), ("b", 37), ("c", 58)])}
+    reference = {rid: plain.forward(config, weights, toks).numpy() for rid, toks in sequences.items()}
+    bound = {rid: (3e-5 * max(1.0, float(np.abs(ref).max())) if dtype == "float32" else 0.05 * float(np.abs(ref).max()))
+             for rid, ref in reference.items()}
+    runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=page, max_tokens=3 * 96, num_slots=4)
+
+    def run(steps):
+        live, done = {}, {rid: 0 for rid in sequences}
+        for step in steps:
+            entries, names = [], []
+            for rid, count in step:
+                if rid not in live:
+                    live[rid] = runner.cache.open((rid, id(steps)))
+                tokens = sequences[rid][done[rid] : done[rid] + count]
+                entries.append(StepEntry(live[rid], tokens, list(range(count))))
+                names.append((rid, done[rid], count))
+                done[rid] += count
+            logits = runner.step(entries).cpu().numpy()
+            row = 0
+            for rid, first, count in names:
+                worst = float(np.abs(logits[row : row + count] - reference[rid][first : first + count]).max())
+                assert worst <= bound[rid], f"{raw}: {rid} at {first}+{count}: max abs diff {worst} (bound {bound[rid]})"
+                row += count
+        for request in live.values():
+            runner.cache.close(request)
+
+    run([[("a", 83)]])
+    run([[("b", 9)], [("b", 2)], [("b", 16)], [("b", 5)]] + [[("b", 1)]] * 5)
+    run([[("a", 30), ("c", 1)], [("c", 1), ("b", 20)], [("a", 1), ("b", 1), ("c", 40)], [("a", 52), ("b", 16), ("c", 16)]])
+    run([[("c", 58), ("a", 2)], [("a", 81), ("b", 37)]])
+
+
 # ---------------------------------------------------------------------- generation
 def _greedy_within_rounding(config, weights, prompt, generated, dtype):
     """Whether every generated token is the plain implementation's choice given the tokens before it, or, in bfloat16,
