@@ -272,13 +272,13 @@ __global__ void token_shift_kernel(const float* __restrict__ h, const float* __r
             for (int j = 0; j < 4; ++j) c[j] += (p[j] - c[j]) * m[j];
             store4<O>(dst + i, c);
         }
-        return;
-    }
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float c = cur[i];
-        const float p = prev[i];
-        if (is_first) kept[i] = end[i];
-        dst[i] = from_f32<O>(c + (p - c) * mu[i]);
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float c = cur[i];
+            const float p = prev[i];
+            if (is_first) kept[i] = end[i];
+            dst[i] = from_f32<O>(c + (p - c) * mu[i]);
+        }
     }
 }
 
@@ -310,11 +310,21 @@ KIRAI_EXPORT int kirai_token_shift_bf16(const float* h, const float* mu, float* 
 // output gate's pre-activations.  z = sigmoid(. + zb); u = . + xb; c = u + 1/2 where u >= 0, sigmoid(u) below;
 // S <- (1 - z) S + z c; out = S * silu(g).
 __device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
+// The same from the fast exponential and division (relative error about 1e-6): for the serving path, whose gates'
+// pre-activations come out of bfloat16 products; the 32-bit path keeps the exact forms.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+template <bool FAST>
+__device__ __forceinline__ float sigmoid_as(float x) { return FAST ? sigmoid_fast(x) : sigmoid_f32(x); }
+template <typename O>
+struct serves_rounded { static constexpr bool value = false; };
+template <>
+struct serves_rounded<bf16> { static constexpr bool value = true; };
 
+template <bool FAST>
 __device__ __forceinline__ void mingru_terms(const float* __restrict__ row, int width, int ch, float zb, float xb, float& z, float& c) {
-    z = sigmoid_f32(row[ch] + zb);
+    z = sigmoid_as<FAST>(row[ch] + zb);
     const float u = row[width + ch] + xb;
-    c = u >= 0.0f ? u + 0.5f : sigmoid_f32(u);
+    c = u >= 0.0f ? u + 0.5f : sigmoid_as<FAST>(u);
 }
 
 // A thread per (request, channel) walks the request's tokens of this step in order.
@@ -332,22 +342,23 @@ __global__ void mingru_walk_kernel(const float* __restrict__ zxg, long row_strid
     const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
     pdl_wait();
     float s = state[(size_t)slot * width + ch];
-#pragma unroll 4
+#pragma unroll 8
     for (int t = first; t < end; ++t) {
         const float* row = zxg + (size_t)t * row_stride;
         float z, c;
-        mingru_terms(row, width, ch, zb, xb, z, c);
+        mingru_terms<serves_rounded<O>::value>(row, width, ch, zb, xb, z, c);
         s = fmaf(z, c - s, s);  // (1 - z) s + z c
         const float g = row[2 * width + ch];
-        out[(size_t)t * width + ch] = from_f32<O>(s * g * sigmoid_f32(g));
+        out[(size_t)t * width + ch] = from_f32<O>(s * g * sigmoid_as<serves_rounded<O>::value>(g));
     }
     state[(size_t)slot * width + ch] = s;
 }
 
-#define SCAN_PIECE 16
+#define SCAN_PIECE 32
 
 // Pieces of SCAN_PIECE tokens, counted from the request's first row of this step.  Pass 1: a thread per (piece,
 // channel) leaves the piece's decay (product of 1 - z) and its end state from a zero start.
+template <bool FAST>
 __global__ void mingru_piece_kernel(const float* __restrict__ zxg, long row_stride, const float* __restrict__ z_bias,
                                     const float* __restrict__ x_bias, const int* __restrict__ query_start,
                                     float* __restrict__ decay, float* __restrict__ ends, int width, int max_pieces) {
@@ -360,10 +371,10 @@ __global__ void mingru_piece_kernel(const float* __restrict__ zxg, long row_stri
     const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
     pdl_wait();
     float a = 1.0f, s = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
     for (int t = first; t < end; ++t) {
         float z, c;
-        mingru_terms(zxg + (size_t)t * row_stride, width, ch, zb, xb, z, c);
+        mingru_terms<FAST>(zxg + (size_t)t * row_stride, width, ch, zb, xb, z, c);
         a *= 1.0f - z;
         s = fmaf(z, c - s, s);
     }
@@ -386,11 +397,22 @@ __global__ void mingru_carry_kernel(const float* __restrict__ decay, float* __re
     if (ch >= width || slot < 0 || slot >= num_slots) return;
     pdl_wait();
     float s = state[(size_t)slot * width + ch];
-    for (int p = 0; p < pieces; ++p) {
-        const size_t at = ((size_t)request * max_pieces + p) * width + ch;
-        const float incoming = s;
-        s = fmaf(decay[at], s, ends[at]);
-        ends[at] = incoming;
+    // eight pieces' terms are asked for at once, so that the chain of multiply-adds does not wait on each load
+    for (int p0 = 0; p0 < pieces; p0 += 8) {
+        float a[8], b[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const size_t at = ((size_t)request * max_pieces + min(p0 + k, pieces - 1)) * width + ch;
+            a[k] = decay[at];
+            b[k] = ends[at];
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (p0 + k < pieces) {
+                ends[((size_t)request * max_pieces + p0 + k) * width + ch] = s;
+                s = fmaf(a[k], s, b[k]);
+            }
+        }
     }
     state[(size_t)slot * width + ch] = s;
 }
@@ -409,14 +431,14 @@ __global__ void mingru_rows_kernel(const float* __restrict__ zxg, long row_strid
     const float zb = z_bias ? z_bias[ch] : 0.0f, xb = x_bias ? x_bias[ch] : 0.0f;
     pdl_wait();
     float s = incoming[((size_t)request * max_pieces + piece) * width + ch];
-#pragma unroll 4
+#pragma unroll 8
     for (int t = first; t < end; ++t) {
         const float* row = zxg + (size_t)t * row_stride;
         float z, c;
-        mingru_terms(row, width, ch, zb, xb, z, c);
+        mingru_terms<serves_rounded<O>::value>(row, width, ch, zb, xb, z, c);
         s = fmaf(z, c - s, s);
         const float g = row[2 * width + ch];
-        out[(size_t)t * width + ch] = from_f32<O>(s * g * sigmoid_f32(g));
+        out[(size_t)t * width + ch] = from_f32<O>(s * g * sigmoid_as<serves_rounded<O>::value>(g));
     }
 }
 
@@ -437,7 +459,7 @@ static int mingru_launch(const float* zxg, long row_stride, const float* z_bias,
     if (max_pieces > 65535) return KIRAI_ERR_BAD_SIZE;
     float* decay = scratch;
     float* ends = scratch + (size_t)requests * max_pieces * width;
-    int status = launch_pdl(mingru_piece_kernel, dim3(blocks, max_pieces, requests), dim3(threads), 0, stream, 1u, zxg, row_stride,
+    int status = launch_pdl(mingru_piece_kernel<serves_rounded<O>::value>, dim3(blocks, max_pieces, requests), dim3(threads), 0, stream, 1u, zxg, row_stride,
                             z_bias, x_bias, query_start, decay, ends, width, max_pieces);
     if (status) return status;
     status = launch_pdl(mingru_carry_kernel, dim3(blocks, requests), dim3(threads), 0, stream, 1u, (const float*)decay, ends, state,
@@ -687,18 +709,18 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ x, const float* __restrict__
             load4<T>(p, v);
             load4<float>(gate + row * gate_stride + col, g);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] *= sigmoid_f32(g[j]);
+            for (int j = 0; j < 4; ++j) v[j] *= sigmoid_as<serves_rounded<T>::value>(g[j]);
             store4<T>(p, v);
         }
-        return;
-    }
-    const long total = rows * per_row;
-    for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
-        const long row = at / per_row;
-        const int col = (int)(at - row * per_row);
-        const int head = col / used, c = col - head * used;
-        T* p = x + (row * heads + head) * dpad + c;
-        *p = from_f32<T>(to_f32<T>(*p) * sigmoid_f32(gate[row * gate_stride + col]));
+    } else {
+        const long total = rows * per_row;
+        for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
+            const long row = at / per_row;
+            const int col = (int)(at - row * per_row);
+            const int head = col / used, c = col - head * used;
+            T* p = x + (row * heads + head) * dpad + c;
+            *p = from_f32<T>(to_f32<T>(*p) * sigmoid_f32(gate[row * gate_stride + col]));
+        }
     }
 }
 
