@@ -24,7 +24,8 @@
 // 8 rows) that leaves a tile as [group][panel][8 rows][128 bytes]; head sizes that are no multiple of 64 and
 // pages under 8 tokens take one request per panel and at most 8 rows into the same layout.
 // Same visibility rule as the other attention kernels: row at position pos sees keys
-// lo <= j <= pos.  head_dim: a multiple of 8 up to 128; the group size must divide 128.
+// lo <= j <= pos.  head_dim: a multiple of 8 up to 256 (above 128: one CTA per SM, all of its tensor memory); the
+// group size must divide 128.
 #include "sm100.cuh"
 #include "tensor_map.cuh"
 
@@ -36,7 +37,13 @@ namespace {
 #define TA_BN 64
 #define TA_STAGES 2   // slots of the K ring, and of the V ring
 #define TA_THREADS 224
-#define TA_TMEM_COLS 256  // S buffers (and, over each one's first half, its P) in columns 0..63 and 64..127, O in 128..255
+// Tensor memory: S buffers (and, over each one's first half, its P) in columns 0..63 and 64..127, O in 128..128 + D - 1.
+// Heads of up to 128 columns need 256 columns, so that two CTAs share an SM; wider heads take all 512 (their shared
+// memory leaves room for one CTA per SM anyway).
+template <int D>
+struct TaTmem {
+    static constexpr uint32_t cols = D <= 128 ? 256u : 512u;
+};
 
 template <int D>
 struct TcAttnSmem {
@@ -188,7 +195,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_addr(tmem_slot), TA_TMEM_COLS);
+        tmem_alloc(smem_addr(tmem_slot), TaTmem<D>::cols);
         tmem_relinquish();
     }
     // Q tile: row r is token (row0 + r) / group, head kv_head * group + (row0 + r) % group
@@ -494,7 +501,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TA_TMEM_COLS);
+        tmem_dealloc(tmem_base, TaTmem<D>::cols);
     }
 }
 
@@ -511,7 +518,7 @@ int launch(const void* q, const void* cache, void* out, const int* block_table, 
     const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
     // whole rows of a box in one request where the sizes allow it; else pieces of one panel and at most 8 rows
     int piece_rows = 0;
-    if (head_dim % 64 != 0 || box_rows % 8 != 0 || !tmap::bf16_kv_boxes_sw128(&kv_map, cache, rows, head_dim, box_rows)) {
+    if (head_dim != D || box_rows % 8 != 0 || !tmap::bf16_kv_boxes_sw128(&kv_map, cache, rows, head_dim, box_rows)) {
         piece_rows = box_rows < 8 ? box_rows : 8;
         if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, piece_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
     }
@@ -528,7 +535,7 @@ int launch(const void* q, const void* cache, void* out, const int* block_table, 
 }  // namespace
 
 // Same arguments as kirai_attention_prefill_bf16.  Refuses (KIRAI_ERR_UNSUPPORTED) head sizes above
-// 128, groups that do not divide 128, and page sizes that are no power of two.
+// 256, groups that do not divide 128, and page sizes that are no power of two.
 static int attention_prefill_tc_entry(const void* q, const void* cache, void* out, const int* block_table,
                                       const int* query_start, const int* context_len, int requests,
                                       int max_query_len, int q_heads, int kv_heads, int head_dim,
@@ -538,13 +545,16 @@ static int attention_prefill_tc_entry(const void* q, const void* cache, void* ou
     if (kv_heads <= 0 || q_heads % kv_heads != 0) return KIRAI_ERR_BAD_SIZE;
     const int group = q_heads / kv_heads;
     if (head_dim <= 0 || head_dim % 8 != 0) return KIRAI_ERR_BAD_SIZE;
-    if (head_dim > 128 || TA_ROWS % group != 0) return KIRAI_ERR_UNSUPPORTED;
+    if (head_dim > 256 || TA_ROWS % group != 0) return KIRAI_ERR_UNSUPPORTED;
     if (q_row_stride % 8 != 0 || ((uintptr_t)q & 15)) return KIRAI_ERR_BAD_ALIGN;
     if (requests > 65535 || kv_heads > 65535) return KIRAI_ERR_BAD_SIZE;
     if (head_dim <= 64)
         return launch<64>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, kv_heads,
                           head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, softcap, error_flag, stream);
-    return launch<128>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, kv_heads,
+    if (head_dim <= 128)
+        return launch<128>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, kv_heads,
+                           head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, softcap, error_flag, stream);
+    return launch<256>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, kv_heads,
                        head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, softcap, error_flag, stream);
 }
 

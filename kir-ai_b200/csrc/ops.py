@@ -765,10 +765,10 @@ def page_size_refusal(dtype: torch.dtype, head_dim: int, page_size: int) -> Opti
 
 
 def attention_prefill_takes_tcgen05(q_heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
-    """Whether the tcgen05 prompt-attention kernel takes this shape: head size up to 128, a group size
-    that divides its 128 query rows, pages of a power-of-two size."""
+    """Whether the tcgen05 prompt-attention kernel takes this shape: head size up to 256 (above 128 a CTA takes a
+    whole SM's tensor memory), a group size that divides its 128 query rows, pages of a power-of-two size."""
     group = q_heads // kv_heads
-    return head_dim <= 128 and head_dim % 8 == 0 and 128 % group == 0 and page_size & (page_size - 1) == 0
+    return head_dim <= 256 and head_dim % 8 == 0 and 128 % group == 0 and page_size & (page_size - 1) == 0
 
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, query_start: torch.Tensor,

@@ -357,6 +357,9 @@ PART_CASES = [
     (latent(6, 10, 6, 12, 20, 18, 1.2, base=300.0, scaling=(2.0, 1.0, 3.0, 16)), 100, 8),
     (latent(20, 16, 16, 8, 32, 48, 0.9), 64, 16),
     (latent(1, 24, 2, 24, 8, 30, 1.0), 40, 2),
+    (latent(8, 32, 64, 32, 64, 192, 0.6), 128, 16),   # a cached row of 256 columns
+    (latent(4, 16, 32, 24, 40, 168, 0.6), 96, 8),     # a row of 200 columns
+    (attn(4, 2, 256, 136, 0.4, rot(10000.0, 64), softcap=15.0, chunk=40), 128, 16),
 ]
 
 
