@@ -499,8 +499,8 @@ def main() -> int:
                              "Qwen3-32B shape.  Both run through Engine.generate and print their own one line.  decode-stamps: "
                              "the kernels' own clock stamps inside one captured decode step (--batch, --context, --layers; "
                              "4 layers are enough), a table instead of the JSON line.  designs: prefill and decode of the "
-                             "Zoferax decoder beside the dense Qwen3 decoder at equal layer sizes (--sizes), with every "
-                             "step's time by kernel; a line of its own.")
+                             "designs named by --designs (default: the Zoferax decoder beside the dense Qwen3 decoder) at "
+                             "equal layer sizes (--sizes), with every step's time by kernel; a line of its own.")
     parser.add_argument("--sizes", default="2k,4k", help="layer sizes of --workload designs: " + ", ".join(DESIGN_SIZES))
     parser.add_argument("--designs", default="zoferax,qwen3-dense",
                         help="which designs --workload designs measures, comma separated: zoferax, silupel, qwen3-dense")

@@ -99,6 +99,16 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
             mma_bf16_16816(s[2 * n2 + 1], a, b2, b3);
         }
     }
+    // a soft cap turns the scores into exponents here, behind a branch that launches without a cap never take, so
+    // that they pay nothing per score; the factor below is then one
+    if (form.cap_log2 != 0.0f) {
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[n][e] = capped_exponent(s[n][e], form);
+        }
+    }
+    const float scale_log2 = form.cap_log2 != 0.0f ? 1.0f : form.scale_log2;
     // mask, running maximum
     const int col0 = j0 + 2 * (lane & 3);
     float m_new[2] = {st.m[0], st.m[1]};
@@ -109,7 +119,7 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
             const int r = e >> 1;
             const int j = col0 + n * 8 + (e & 1);
             const bool visible = j >= lo[r] && j <= hi[r];
-            s[n][e] = visible ? score_exponent(s[n][e], form) : -INFINITY;
+            s[n][e] = visible ? s[n][e] * scale_log2 : -INFINITY;
             m_new[r] = fmaxf(m_new[r], s[n][e]);
         }
     }
@@ -455,6 +465,15 @@ __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32
     // mask by key position (rows g and g + 8 of each m-tile), running maximum per head
     const int g = lane >> 2;
     const bool interior = j0 >= lo && j0 + BN - 1 <= hi;
+    // (a soft cap behind a branch of its own, as in warp_attend)
+    if (form.cap_log2 != 0.0f) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[mt][e] = capped_exponent(s[mt][e], form);
+        }
+    }
+    const float scale_log2 = form.cap_log2 != 0.0f ? 1.0f : form.scale_log2;
     float m_new[2] = {st.m[0], st.m[1]};
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -462,7 +481,7 @@ __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32
         for (int e = 0; e < 4; ++e) {
             const int j = j0 + mt * 16 + g + (e >> 1) * 8;
             const bool visible = interior || (j >= lo && j <= hi);
-            s[mt][e] = visible ? score_exponent(s[mt][e], form) : -INFINITY;
+            s[mt][e] = visible ? s[mt][e] * scale_log2 : -INFINITY;
             m_new[e & 1] = fmaxf(m_new[e & 1], s[mt][e]);
         }
     }

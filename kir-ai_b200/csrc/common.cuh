@@ -114,10 +114,6 @@ __device__ __forceinline__ float capped_exponent(float raw, const ScoreForm& for
     return fmaf(form.cap_out, r, form.cap_log2);
 }
 
-__device__ __forceinline__ float score_exponent(float raw, const ScoreForm& form) {
-    return form.cap_log2 != 0.0f ? capped_exponent(raw, form) : raw * form.scale_log2;
-}
-
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // ---- programmatic dependent launch -----------------------------------------
